@@ -1,4 +1,5 @@
 from .spec import (ConfigError, LayerSpec, ModelSpec, PartSpec, ScheduleEntry)
 from .qwen3 import Qwen3Config
+from .nuvilorn import NuvilornConfig
 
-__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config"]
+__all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "NuvilornConfig"]

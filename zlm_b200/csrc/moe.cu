@@ -1,0 +1,233 @@
+// Routed feed-forward (mixture of experts), the plain kernels for both element types and every size:
+//   moe_route     per token: router logits z = W_r h in fp32, scores sigmoid(z) (or softmax), the `top`
+//                 largest (ties to the lower index) with their scores as weights; optionally a gate
+//                 sigmoid(w_g . h) for a shared expert
+//   moe_up        a[t, j, f] = act(w_tj * (W_up[e_tj] h_t)[f]): the weight scales the expert's input, which
+//                 for a bias-free expert is the same as scaling its first product
+//   moe_down      stream[t, :] += sum_j W_down[e_tj] a[t, j, :], experts in the order they were chosen
+//   act_scale     out[t, i] = act(u[t, i]) * s[t]  (a shared expert between the library's dense products)
+// act is relu(z)^2.  A warp owns one output and shares the inner dimension among its lanes, so every sum's
+// order depends on the sizes alone, not on the batch.
+#include "common.cuh"
+
+// eight consecutive elements from 16-byte aligned storage as floats
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
+    const uint4 v = *(const uint4*)p;
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+__device__ __forceinline__ void load8(const float* p, float* f) {
+    const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// sum_k w[k] x[k] by one warp; `vec`: K % 8 == 0 and both rows 16-byte aligned
+template <typename TA>
+__device__ __forceinline__ float warp_dot(const TA* __restrict__ w, const TA* __restrict__ x, int K, int lane, bool vec) {
+    float acc = 0.f;
+    if (vec) {
+        for (int k = lane * 8; k < K; k += 256) {
+            if (!ZLM_CHK(w + k, 8 * sizeof(TA)) || !ZLM_CHK(x + k, 8 * sizeof(TA))) continue;
+            float a[8], b[8];
+            load8(w + k, a);
+            load8(x + k, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(a[i], b[i], acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32)
+            if (ZLM_CHK(w + k, sizeof(TA)) && ZLM_CHK(x + k, sizeof(TA))) acc = fmaf(to_f32(w[k]), to_f32(x[k]), acc);
+    }
+    return warp_sum(acc);
+}
+
+template <typename TA>
+__device__ __forceinline__ bool rows_vectorise(const TA* a, const TA* b, int K, size_t lda, size_t ldb) {
+    return K % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)b % 16 == 0 && (lda * sizeof(TA)) % 16 == 0 &&
+           (ldb * sizeof(TA)) % 16 == 0;
+}
+
+// ---------------------------------------------------------------------------- router
+#define ROUTE_WARPS 4
+// score_kind 0: sigmoid of each logit; 1: softmax over the experts.  renorm: the chosen weights divided by their sum.
+template <typename TA>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restrict__ gate, const TA* __restrict__ x,
+                 int x_stride, const TA* __restrict__ Wr, const TA* __restrict__ wg, int E, int K, int top,
+                 int score_kind, int renorm) {
+    extern __shared__ float sc[];           // [E]
+    pdl_trigger();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const TA* xr = x + (size_t)t * x_stride;
+    pdl_wait();
+    const bool vec = rows_vectorise(Wr, xr, K, (size_t)K, (size_t)x_stride) && (wg == nullptr || (uintptr_t)wg % 16 == 0);
+    for (int e = warp; e < E + (wg ? 1 : 0); e += ROUTE_WARPS) {
+        const float z = warp_dot(e < E ? Wr + (size_t)e * K : wg, xr, K, lane, vec);
+        if (lane == 0) {
+            if (e < E) sc[e] = score_kind == 0 ? 1.0f / (1.0f + expf(-z)) : z;
+            else if (ZLM_CHK(gate + t, 4)) gate[t] = 1.0f / (1.0f + expf(-z));
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (score_kind == 1) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = 0; e < E; ++e) sum += expf(sc[e] - mx);      // one order for all lanes
+        for (int e = lane; e < E; e += 32) sc[e] = expf(sc[e] - mx) / sum;
+        __syncwarp();
+    }
+    float chosen_sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[e];
+            if (v > bv) { bv = v; bi = e; }        // ascending e: ties keep the lower index
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0 && ZLM_CHK(idx + (size_t)t * top + j, 4) && ZLM_CHK(wgt + (size_t)t * top + j, 4)) {
+            idx[(size_t)t * top + j] = bi;
+            wgt[(size_t)t * top + j] = bv;
+            sc[bi] = -INFINITY;
+        }
+        chosen_sum += bv;
+        __syncwarp();
+    }
+    if (renorm && lane == 0)
+        for (int j = 0; j < top; ++j) wgt[(size_t)t * top + j] /= chosen_sum;
+}
+
+extern "C" int zlm_moe_route(int* idx, float* wgt, float* gate, const void* x, int x_stride, const void* Wr,
+                             const void* wg, int dtype, int T, int E, int K, int top, int score_kind, int renorm,
+                             cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(E > 0 && E <= 8192 && K > 0 && top > 0 && top <= E, "moe_route: experts=%d top=%d K=%d", E, top, K);
+    ZLM_REQUIRE(score_kind == 0 || score_kind == 1, "moe_route: score kind %d", score_kind);
+    ZLM_REQUIRE(wg == nullptr || gate != nullptr, "moe_route: a shared gate needs a place for its values");
+    const size_t smem = (size_t)E * sizeof(float);
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(moe_route_kernel<float>, T, ROUTE_WARPS * 32, smem, st, idx, wgt, gate, (const float*)x, x_stride,
+                   (const float*)Wr, (const float*)wg, E, K, top, score_kind, renorm);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(moe_route_kernel<__nv_bfloat16>, T, ROUTE_WARPS * 32, smem, st, idx, wgt, gate, (const __nv_bfloat16*)x,
+                   x_stride, (const __nv_bfloat16*)Wr, (const __nv_bfloat16*)wg, E, K, top, score_kind, renorm);
+    else
+        ZLM_REQUIRE(false, "moe_route: unsupported dtype %d", dtype);
+    return zlm_check_launch("moe_route");
+}
+
+// ---------------------------------------------------------------------------- experts, token by token
+__device__ __forceinline__ float relu2(float z) { z = fmaxf(z, 0.f); return z * z; }
+
+#define MOE_WARPS 8
+// act[t, j, f] = relu(w[t, j] * (Wup[idx[t, j]][f, :] . x[t]))^2;  grid (ceil(F / MOE_WARPS), top, T)
+template <typename TA>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_up_kernel(TA* __restrict__ act, const TA* __restrict__ x, int x_stride, const TA* __restrict__ Wup,
+              const int* __restrict__ idx, const float* __restrict__ wgt, int top, int F, int K, int scale_input) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int f = blockIdx.x * MOE_WARPS + warp, j = blockIdx.y, t = blockIdx.z;
+    if (f >= F) return;
+    pdl_wait();
+    if (!ZLM_CHK(idx + (size_t)t * top + j, 4) || !ZLM_CHK(wgt + (size_t)t * top + j, 4)) return;
+    const int e = idx[(size_t)t * top + j];
+    const float w = wgt[(size_t)t * top + j];
+    const TA* wr = Wup + ((size_t)e * F + f) * K;
+    const TA* xr = x + (size_t)t * x_stride;
+    const float z = warp_dot(wr, xr, K, lane, rows_vectorise(Wup, xr, K, (size_t)K, (size_t)x_stride));
+    if (lane == 0 && ZLM_CHK(act + ((size_t)t * top + j) * F + f, sizeof(TA)))
+        act[((size_t)t * top + j) * F + f] = from_f32<TA>(scale_input ? relu2(w * z) : w * relu2(z));
+}
+
+// stream[t, n] += sum_j Wdown[idx[t, j]][n, :] . act[t, j, :];  grid (ceil(N / MOE_WARPS), T)
+template <typename TA>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_down_kernel(float* __restrict__ stream, const TA* __restrict__ act, const TA* __restrict__ Wdown,
+                const int* __restrict__ idx, int top, int F, int N) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x * MOE_WARPS + warp, t = blockIdx.y;
+    if (n >= N) return;
+    pdl_wait();
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+        if (!ZLM_CHK(idx + (size_t)t * top + j, 4)) continue;
+        const int e = idx[(size_t)t * top + j];
+        const TA* wr = Wdown + ((size_t)e * N + n) * F;
+        const TA* ar = act + ((size_t)t * top + j) * F;
+        sum += warp_dot(wr, ar, F, lane, rows_vectorise(Wdown, act, F, (size_t)F, (size_t)F));
+    }
+    if (lane == 0 && ZLM_CHK(stream + (size_t)t * N + n, 4)) stream[(size_t)t * N + n] += sum;
+}
+
+extern "C" int zlm_moe_up(void* act, const void* x, int x_stride, const void* Wup, const int* idx, const float* wgt,
+                          int dtype, int T, int top, int F, int K, int scale_input, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(T <= 65535 && top > 0 && top <= 65535 && F > 0 && K > 0, "moe_up: bad sizes T=%d top=%d F=%d K=%d", T, top, F, K);
+    dim3 grid((F + MOE_WARPS - 1) / MOE_WARPS, top, T);
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(moe_up_kernel<float>, grid, MOE_WARPS * 32, 0, st, (float*)act, (const float*)x, x_stride,
+                   (const float*)Wup, idx, wgt, top, F, K, scale_input);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(moe_up_kernel<__nv_bfloat16>, grid, MOE_WARPS * 32, 0, st, (__nv_bfloat16*)act, (const __nv_bfloat16*)x,
+                   x_stride, (const __nv_bfloat16*)Wup, idx, wgt, top, F, K, scale_input);
+    else
+        ZLM_REQUIRE(false, "moe_up: unsupported dtype %d", dtype);
+    return zlm_check_launch("moe_up");
+}
+
+extern "C" int zlm_moe_down(float* stream, const void* act, const void* Wdown, const int* idx, int dtype, int T, int top,
+                            int F, int N, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(T <= 65535 && top > 0 && F > 0 && N > 0, "moe_down: bad sizes T=%d top=%d F=%d N=%d", T, top, F, N);
+    dim3 grid((N + MOE_WARPS - 1) / MOE_WARPS, T);
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(moe_down_kernel<float>, grid, MOE_WARPS * 32, 0, st, stream, (const float*)act, (const float*)Wdown, idx,
+                   top, F, N);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(moe_down_kernel<__nv_bfloat16>, grid, MOE_WARPS * 32, 0, st, stream, (const __nv_bfloat16*)act,
+                   (const __nv_bfloat16*)Wdown, idx, top, F, N);
+    else
+        ZLM_REQUIRE(false, "moe_down: unsupported dtype %d", dtype);
+    return zlm_check_launch("moe_down");
+}
+
+// ---------------------------------------------------------------------------- activation with a row scale
+template <typename TA>
+__global__ void act_scale_kernel(TA* __restrict__ out, const TA* __restrict__ u, const float* __restrict__ s, int T, int F) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t n = (size_t)T * F;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / F;
+        if (!ZLM_CHK(u + e, sizeof(TA)) || !ZLM_CHK(out + e, sizeof(TA)) || (s && !ZLM_CHK(s + t, 4))) continue;
+        out[e] = from_f32<TA>(relu2(to_f32(u[e])) * (s ? s[t] : 1.0f));
+    }
+}
+
+extern "C" int zlm_relu2_scale(void* out, const void* u, const float* s, int dtype, int T, int F, cudaStream_t st) {
+    if (T == 0 || F == 0) return ZLM_OK;
+    const size_t n = (size_t)T * F;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(act_scale_kernel<float>, blocks, 256, 0, st, (float*)out, (const float*)u, s, T, F);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(act_scale_kernel<__nv_bfloat16>, blocks, 256, 0, st, (__nv_bfloat16*)out, (const __nv_bfloat16*)u, s, T, F);
+    else
+        ZLM_REQUIRE(false, "relu2_scale: unsupported dtype %d", dtype);
+    return zlm_check_launch("relu2_scale");
+}
+
+ZLM_TRANSLATION_UNIT(moe)

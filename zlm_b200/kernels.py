@@ -653,6 +653,113 @@ class CudaKernels:
                    self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
                    c_int(nkv), c_int(hd), c_float(scale), c_int(window), self._stream())
 
+    # -- latent attention (see csrc/latent_attention.cu) --------------------
+    def latent_prep(self, q: torch.Tensor, q_rot: torch.Tensor, dkv: Optional[torch.Tensor],
+                    c_weight: Optional[torch.Tensor], eps: float,
+                    inv_freq: Optional[torch.Tensor], n_rot: int, token_pos: torch.Tensor, token_slot: torch.Tensor,
+                    block_table: Optional[torch.Tensor], pool: Optional[torch.Tensor], heads: int, dim: int,
+                    rot_dim: int, kv_rank: int) -> None:
+        """Per token: the rotated parts of the heads' queries (q [T, heads * (dim + rot_dim)], each head
+        [dim | rot_dim]) are turned by the token's position, neighbouring pairs (2i, 2i+1) by
+        pos * inv_freq[i], and written to q_rot [T, heads, rot_dim] (any token and head strides; it may
+        be the view q[:, :, dim:] itself); and, where ``dkv`` [T, kv_rank + rot_dim] is given, the token's record
+        [RMSNorm(dkv[:kv_rank]) * c_weight | rotated dkv[kv_rank:]] goes to its place in the paged
+        ``pool`` [pages, PAGE_TOKENS, kv_rank + rot_dim]."""
+        T = q.shape[0]
+        assert q.shape[1] == heads * (dim + rot_dim) and q.stride(1) == 1
+        assert q_rot.shape == (T, heads, rot_dim) and q_rot.dtype == q.dtype and (rot_dim == 0 or q_rot.stride(2) == 1)
+        if inv_freq is not None:
+            assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot
+        else:
+            n_rot = 0
+        if dkv is not None:
+            assert dkv.shape == (T, kv_rank + rot_dim) and dkv.stride(1) == 1 and dkv.dtype == q.dtype
+            assert pool is not None and pool.dtype == q.dtype and pool.is_contiguous()
+            assert tuple(pool.shape[1:]) == (PAGE_TOKENS, kv_rank + rot_dim) and block_table.dtype == torch.int32
+            assert c_weight is not None and c_weight.shape == (kv_rank,) and c_weight.is_contiguous()
+        self._call("zlm_latent_prep", self._p(q), c_int(q.stride(0)), self._p(q_rot), c_int(q_rot.stride(0)),
+                   c_int(q_rot.stride(1)), self._p(dkv),
+                   c_int(dkv.stride(0) if dkv is not None else 0), c_int(_dt(q)), self._p(c_weight if dkv is not None else None),
+                   c_int(_dt(c_weight) if dkv is not None else F32), c_float(eps), self._p(inv_freq), c_int(n_rot),
+                   self._p(token_pos), self._p(token_slot), self._p(block_table if dkv is not None else None),
+                   c_int(block_table.stride(0) if dkv is not None else 0), self._p(pool if dkv is not None else None),
+                   c_int(T), c_int(heads), c_int(dim), c_int(rot_dim), c_int(kv_rank), self._stream())
+
+    def head_linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
+        """out[t, h, :] = w[h] @ x[t, h, :] for per-head matrices w [heads, N, K]; x [T, heads, K] and out
+        [T, heads, N] may be views with any token and head strides (innermost contiguous)."""
+        T, H, K = x.shape
+        N = w.shape[1]
+        assert w.shape == (H, N, K) and w.is_contiguous() and out.shape == (T, H, N)
+        assert x.dtype == w.dtype == out.dtype and x.stride(2) == 1 and out.stride(2) == 1
+        self._call("zlm_head_linear", self._p(out), c_int(out.stride(0)), c_int(out.stride(1)), self._p(x),
+                   c_int(x.stride(0)), c_int(x.stride(1)), self._p(w), c_int(_dt(x)), c_int(T), c_int(H), c_int(N),
+                   c_int(K), self._stream())
+
+    def latent_attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
+                         token_pos: torch.Tensor, token_slot: torch.Tensor, heads: int, kv_rank: int, rot_dim: int,
+                         scale: float, window: int = 0, plan=None, len_bucket: Optional[int] = None) -> None:
+        """out[t, h, :kv_rank] = sum_j softmax_j(q[t, h] . rec_j * scale) rec_j[:kv_rank] over the records
+        [start, pos[t]] of the token's slot in ``pool`` [pages, PAGE_TOKENS, kv_rank + rot_dim]: one
+        key/value record per token that every head reads (q [T, heads * (kv_rank + rot_dim)])."""
+        T = q.shape[0]
+        D = kv_rank + rot_dim
+        assert q.shape[1] == heads * D and out.shape == (T, heads * kv_rank) and q.dtype == out.dtype == pool.dtype
+        assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
+        assert tuple(pool.shape[1:]) == (PAGE_TOKENS, D)
+        self._call("zlm_latent_attention", self._p(out), c_int(out.stride(0)), self._p(q), c_int(q.stride(0)),
+                   c_int(_dt(q)), self._p(pool), self._p(block_table), c_int(block_table.stride(0)),
+                   self._p(token_pos), self._p(token_slot), c_int(T), c_int(heads), c_int(kv_rank), c_int(rot_dim),
+                   c_float(scale), c_int(window), self._stream())
+
+    # -- routed experts (see csrc/moe.cu) -------------------------------------
+    def moe_route(self, idx: torch.Tensor, wgt: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, top: int,
+                  gate: Optional[torch.Tensor] = None, w_gate: Optional[torch.Tensor] = None,
+                  score: str = "sigmoid", renormalize: bool = False) -> None:
+        """idx / wgt [T, top]: the experts with the largest scores of W_router x (fp32 logits; ``score``
+        "sigmoid" or "softmax") and those scores (divided by their sum if ``renormalize``); gate [T] =
+        sigmoid(w_gate . x) where a shared expert has a gate."""
+        T, K = x.shape
+        E = w_router.shape[0]
+        assert w_router.shape == (E, K) and w_router.is_contiguous() and w_router.dtype == x.dtype and x.stride(1) == 1
+        assert idx.dtype == torch.int32 and wgt.dtype == torch.float32 and idx.is_contiguous() and wgt.is_contiguous()
+        assert idx.shape == (T, top) and wgt.shape == (T, top)
+        if w_gate is not None:
+            assert w_gate.numel() == K and w_gate.is_contiguous() and w_gate.dtype == x.dtype
+            assert gate is not None and gate.dtype == torch.float32 and gate.numel() >= T
+        self._call("zlm_moe_route", self._p(idx), self._p(wgt), self._p(gate if w_gate is not None else None), self._p(x),
+                   c_int(x.stride(0)), self._p(w_router), self._p(w_gate), c_int(_dt(x)), c_int(T), c_int(E), c_int(K),
+                   c_int(top), c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0), self._stream())
+
+    def moe_up(self, act: torch.Tensor, x: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor,
+               scale_input: bool = True) -> None:
+        """act[t, j, :] = relu(W_up[idx[t, j]] (wgt[t, j] x[t]))^2 (``scale_input``), or wgt[t, j] * relu(W_up[..] x[t])^2;
+        w_up [experts, F, K], act [T, top, F]."""
+        T, K = x.shape
+        E, F, _ = w_up.shape
+        top = idx.shape[1]
+        assert w_up.shape == (E, F, K) and w_up.is_contiguous() and act.shape == (T, top, F) and act.is_contiguous()
+        assert x.dtype == w_up.dtype == act.dtype and x.stride(1) == 1
+        self._call("zlm_moe_up", self._p(act), self._p(x), c_int(x.stride(0)), self._p(w_up), self._p(idx), self._p(wgt),
+                   c_int(_dt(x)), c_int(T), c_int(top), c_int(F), c_int(K), c_int(1 if scale_input else 0), self._stream())
+
+    def moe_down(self, stream: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor) -> None:
+        """stream[t] += sum_j W_down[idx[t, j]] act[t, j]; w_down [experts, N, F], stream fp32 [T, N]."""
+        T, top, F = act.shape
+        E, N, _ = w_down.shape
+        assert w_down.shape == (E, N, F) and w_down.is_contiguous() and act.is_contiguous() and act.dtype == w_down.dtype
+        assert stream.dtype == torch.float32 and stream.shape == (T, N) and stream.is_contiguous()
+        self._call("zlm_moe_down", self._p(stream), self._p(act), self._p(w_down), self._p(idx), c_int(_dt(act)), c_int(T),
+                   c_int(top), c_int(F), c_int(N), self._stream())
+
+    def relu2_scale(self, out: torch.Tensor, u: torch.Tensor, row_scale: Optional[torch.Tensor] = None) -> None:
+        """out[t, i] = relu(u[t, i])^2 * row_scale[t]."""
+        T, F = u.shape
+        assert out.shape == (T, F) and out.dtype == u.dtype and out.is_contiguous() and u.is_contiguous()
+        assert row_scale is None or (row_scale.dtype == torch.float32 and row_scale.numel() >= T)
+        self._call("zlm_relu2_scale", self._p(out), self._p(u), self._p(row_scale), c_int(_dt(u)), c_int(T), c_int(F),
+                   self._stream())
+
     def argmax(self, out: torch.Tensor, logits: torch.Tensor, fresh: bool = False) -> None:
         """out[r] = index of the highest logit of row r, ties to the lowest index.  ``fresh``: the
         caller vouches that ``logits`` is what ``linear`` wrote last into this tensor and nothing

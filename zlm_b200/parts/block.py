@@ -57,8 +57,14 @@ class PreNormBlock(Part):
             by_products(self.mixer.reads_input_by_products)
         self.mixer_norm.forward(x, hidden)
         if expect is not None:
-            expect(getattr(self.ffn_norm, "weight", None) if self.ffn_norm.reads_stream_by_kernel else None)
+            after_mixer = (ctx.extras.get("norm_after_block") if getattr(self.ffn, "is_identity", False)
+                           else getattr(self.ffn_norm, "weight", None) if self.ffn_norm.reads_stream_by_kernel else None)
+            expect(after_mixer)
         self.mixer.forward(x, hidden, ctx, io)
+        if getattr(self.ffn, "is_identity", False):        # a layer without a feed-forward
+            if expect is not None:
+                expect(None)
+            return
         if not self.ffn_norm.reads_stream_by_kernel:
             self.finish_products()
         if by_products is not None:

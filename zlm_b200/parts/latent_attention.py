@@ -1,0 +1,123 @@
+"""Latent attention: keys and values of every head are projections of one small latent per
+token, and only that latent is cached.
+
+With h the mixer's input, per token:
+
+    q = W_q h                        per head [dim | rot_dim]: a plain part and a rotated part
+    [c_raw | kr_raw] = W_dkv h       kv_rank + rot_dim rows
+    c  = RMSNorm(c_raw) * w_c        the latent (weight per coordinate)
+    kr = rot(kr_raw, pos)            one rotated key part, shared by all heads
+    k_h = [W_uk_h c | kr],  v_h = W_uv_h c
+    score_h(i, j) = (q_h(i) . k_h(j)) * scale,  j in the window ending at i;  softmax;  y = W_o [heads' outputs]
+
+The cache record of a token is [c | kr] (``CacheRequest.token_shape``); a layer built with
+``kv_proj=False`` has no W_dkv and reads the records of the schedule entry its own entry names
+(``ScheduleEntry.cache_of``), with its own W_uk, W_uv, queries and everything else.
+
+The step folds the up-projections away from the cached side: q'_h = W_uk_h^T q_h[:dim] makes the
+score q'_h . c + rot(q_h[dim:]) . kr, and sum_j p_j v_h(j) = W_uv_h (sum_j p_j c_j), so attention
+runs over the records as they are: one key/value record per token that all heads read.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Mapping, Optional
+
+import torch
+
+from ..registry import POSITION_ENCODINGS, lookup, register_mixer
+from .base import CacheRequest, LayerIO, Mixer, ParamSpec, StepContext
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_dim: int, kv_rank: int,
+                 scale: float, norm_eps: float = 1e-6, window: int = 0,
+                 position: Optional[Mapping[str, Any]] = None, kv_proj: bool = True):
+        self.hidden = int(hidden_size)
+        self.H, self.dn, self.dr, self.dv, self.r = int(num_heads), int(head_dim), int(rot_dim), int(v_dim), int(kv_rank)
+        if min(self.H, self.dv, self.r) <= 0 or self.dn < 0 or self.dr < 0 or self.dn + self.dr <= 0:
+            raise ValueError("latent attention: heads, v_dim, kv_rank and dim + rot_dim must be positive")
+        self.scale, self.eps, self.window = float(scale), float(norm_eps), int(window)
+        self.kv_proj = bool(kv_proj)
+        position = dict(position or {"kind": "none"})
+        self.position = lookup(POSITION_ENCODINGS, "position encoding", position.pop("kind"))(**position)
+        if not getattr(self.position, "fused", False) or not (getattr(self.position, "interleaved", False)
+                                                               or self.position.n_rot == 0):
+            raise ValueError("latent attention rotates neighbouring pairs in its own kernel: "
+                             "position must be 'rope_interleaved' or 'none'")
+        if self.position.n_rot > self.dr:
+            raise ValueError(f"latent attention: {self.position.n_rot} rotated dimensions in a part of {self.dr}")
+        self.Dq, self.R = self.dn + self.dr, self.r + self.dr
+        self.Q = self.H * self.Dq
+
+    # ---- declarations -----------------------------------------------------
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        s = {"q": ParamSpec((self.Q, self.hidden)),
+             "uk": ParamSpec((self.H * self.dn, self.r)),
+             "uv": ParamSpec((self.H * self.dv, self.r)),
+             "o": ParamSpec((self.hidden, self.H * self.dv))}
+        if self.kv_proj:
+            s["dkv"] = ParamSpec((self.R, self.hidden))
+            s["dkv.norm"] = ParamSpec((self.r,), kind="vector", init="one_plus_normal")
+        return s
+
+    def cache_request(self) -> Optional[CacheRequest]:
+        return CacheRequest(1, self.R, self.window, token_shape=(self.R,))
+
+    def attach(self, rt) -> None:
+        super().attach(rt)
+        self.position.attach(rt)
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        H, dn, dv, r = self.H, self.dn, self.dv, self.r
+        w_q = params.pop("q")
+        if self.kv_proj:
+            # one fused projection: rows [q | c_raw | kr_raw]
+            self.w_in = torch.cat([w_q, params.pop("dkv")], dim=0).contiguous()
+            self.c_norm = params.pop("dkv.norm")
+        else:
+            self.w_in, self.c_norm = w_q, None
+        # per head: W_uk_h^T [r, dn] (folds into the query), W_uv_h [dv, r] (unfolds the output)
+        self.w_uk_t = params.pop("uk").view(H, dn, r).transpose(1, 2).contiguous()
+        self.w_uv = params.pop("uv").view(H, dv, r).contiguous()
+        self.w_o = params.pop("o")
+        self.check_products(q=self.w_in, o=self.w_o)
+
+    def tensors(self) -> Dict[str, torch.Tensor]:
+        out = {"q": self.w_in[: self.Q], "o": self.w_o,
+               "uk": self.w_uk_t.transpose(1, 2).reshape(self.H * self.dn, self.r),
+               "uv": self.w_uv.reshape(self.H * self.dv, self.r)}
+        if self.kv_proj:
+            out["dkv"] = self.w_in[self.Q:]
+            out["dkv.norm"] = self.c_norm
+        return out
+
+    # ---- the step -----------------------------------------------------------
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
+        rt, k = self.rt, self.rt.k
+        T = x.shape[0]
+        H, dn, dr, dv, r, R = self.H, self.dn, self.dr, self.dv, self.r, self.R
+        cache = io.cache
+        writes = cache.writes and self.kv_proj
+        if cache.writes != self.kv_proj:
+            raise ValueError("latent attention: a layer without W_dkv must read another entry's cache, "
+                             "and one with W_dkv keeps its own")
+        qd = rt.ws.get("lat.qd", (T, self.Q + (R if writes else 0)), rt.dtype)
+        k.linear(qd, x, self.w_in)
+        q = qd[:, : self.Q]
+        q3 = q.view(T, H, self.Dq) if not writes else qd.as_strided((T, H, self.Dq), (qd.stride(0), self.Dq, 1))
+        # the folded query [q' | rotated part] of every head
+        ql = rt.ws.get("lat.ql", (T, H, R), rt.dtype)
+        k.latent_prep(q, ql[:, :, r:], qd[:, self.Q:] if writes else None, self.c_norm, self.eps,
+                      self.position.inv_freq, self.position.n_rot, ctx.token_pos, ctx.token_slot,
+                      cache.block_table, cache.pool, H, dn, dr, r)
+        if dn:
+            k.head_linear(ql[:, :, :r], q3[:, :, :dn], self.w_uk_t)
+        else:
+            ql[:, :, :r].zero_()
+        ol = rt.ws.get("lat.ol", (T, H * r), rt.dtype)
+        k.latent_attention(ol, ql.view(T, H * R), cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot,
+                           H, r, dr, self.scale, self.window, ctx)
+        ov = rt.ws.get("lat.ov", (T, H * dv), rt.dtype)
+        k.head_linear(ov.view(T, H, dv), ol.view(T, H, r), self.w_uv)
+        k.linear(residual, ov, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next

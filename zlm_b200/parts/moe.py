@@ -1,0 +1,98 @@
+"""Routed feed-forward: many small experts of which every token uses a few, and optionally one
+shared expert that every token uses.
+
+    z = W_router h (fp32),  s = sigmoid(z) (or softmax over the experts)
+    the ``top_k`` experts with the largest s are chosen; their weights are those s, as they are
+        (or divided by their sum: ``renormalize``)
+    expert(u) = W_down act(W_up u), act(z) = relu(z)^2, no biases
+    y = sum_e expert_e(w_e h)                 the weight scales the expert's input (``weight_on="input"``)
+        or sum_e w_e expert_e(h)              (``weight_on="output"``)
+      + sigmoid(w_sg . h) * shared(h)         the shared expert, if any, with a gate of one number per token
+                                              (``shared_gate``; without it the shared expert is added as it is)
+
+The experts' matrices are kept stacked, [experts, ff, hidden] and [experts, hidden, ff], so that a
+kernel reaches an expert by its index; the checkpoint has them one by one (``e<i>.up``, ``e<i>.down``).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..registry import register_feed_forward
+from .base import FeedForward, ParamSpec, StepContext
+
+
+@register_feed_forward("none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: the arrangement skips it and its norm."""
+    is_identity = True
+
+    def __init__(self, hidden_size: int):
+        self.hidden = int(hidden_size)
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        return
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_ff: int, shared_ff: int = 0,
+                 shared_gate: bool = True, score: str = "sigmoid", renormalize: bool = False,
+                 weight_on: str = "input"):
+        self.hidden, self.E, self.top, self.F = int(hidden_size), int(num_experts), int(top_k), int(expert_ff)
+        self.SF, self.shared_gate = int(shared_ff), bool(shared_gate) and int(shared_ff) > 0
+        if not 0 < self.top <= self.E:
+            raise ValueError(f"routed experts: top_k={self.top} of {self.E} experts")
+        if score not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
+            raise ValueError(f"routed experts: score={score!r}, weight_on={weight_on!r}")
+        self.score, self.renormalize, self.scale_input = score, bool(renormalize), weight_on == "input"
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        s = {"router": ParamSpec((self.E, self.hidden))}
+        for e in range(self.E):
+            s[f"e{e}.up"] = ParamSpec((self.F, self.hidden))
+            s[f"e{e}.down"] = ParamSpec((self.hidden, self.F))
+        if self.SF:
+            s["shared.up"] = ParamSpec((self.SF, self.hidden))
+            s["shared.down"] = ParamSpec((self.hidden, self.SF))
+            if self.shared_gate:
+                s["shared.sg"] = ParamSpec((1, self.hidden))
+        return s
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        self.w_router = params.pop("router")
+        self.w_up = torch.stack([params.pop(f"e{e}.up") for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([params.pop(f"e{e}.down") for e in range(self.E)]).contiguous()
+        self.w_sup = self.w_sdown = self.w_sg = None
+        if self.SF:
+            self.w_sup, self.w_sdown = params.pop("shared.up"), params.pop("shared.down")
+            self.w_sg = params.pop("shared.sg") if self.shared_gate else None
+            self.check_products(shared_up=self.w_sup, shared_down=self.w_sdown)
+
+    def tensors(self) -> Dict[str, torch.Tensor]:
+        out = {"router": self.w_router}
+        for e in range(self.E):
+            out[f"e{e}.up"], out[f"e{e}.down"] = self.w_up[e], self.w_down[e]
+        if self.SF:
+            out["shared.up"], out["shared.down"] = self.w_sup, self.w_sdown
+            if self.shared_gate:
+                out["shared.sg"] = self.w_sg
+        return out
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        rt, k = self.rt, self.rt.k
+        T = x.shape[0]
+        idx = rt.ws.get("moe.idx", (T, self.top), torch.int32)
+        wgt = rt.ws.get("moe.wgt", (T, self.top), torch.float32)
+        gate = rt.ws.get("moe.gate", (T,), torch.float32) if self.shared_gate else None
+        k.moe_route(idx, wgt, x, self.w_router, self.top, gate, self.w_sg, self.score, self.renormalize)
+        act = rt.ws.get("moe.act", (T, self.top, self.F), rt.dtype)
+        k.moe_up(act, x, self.w_up, idx, wgt, self.scale_input)
+        k.moe_down(residual, act, self.w_down, idx)
+        if self.SF:
+            u = rt.ws.get("moe.shared_u", (T, self.SF), rt.dtype)
+            k.linear(u, x, self.w_sup)
+            a = rt.ws.get("moe.shared_a", (T, self.SF), rt.dtype)
+            k.relu2_scale(a, u, gate)
+            k.linear(residual, a, self.w_sdown, accumulate=True, defer=True)     # a norm reads the stream next

@@ -48,6 +48,29 @@ class RotaryHalfSplit(PositionEncoding):
         return t
 
 
+@register_position_encoding("rope_interleaved")
+class RotaryInterleaved(PositionEncoding):
+    """Rotary encoding on neighbouring pairs (2i, 2i + 1), i < dims / 2: the pair is turned by
+    pos * base^(-2i / dims); what lies beyond ``dims`` in the rotated vector passes unchanged.  The
+    part carries the table of frequencies (computed in 64-bit, rounded to fp32); the mixer's own
+    kernel forms the angle, its sine and cosine in fp32."""
+    fused = True
+    interleaved = True
+
+    def __init__(self, base: float, dims: int):
+        self.base = float(base)
+        self.n_rot = int(dims)
+        if self.n_rot % 2 or self.n_rot < 0:
+            raise ValueError(f"rope: dims={self.n_rot} must be even")
+        self.inv_freq: Optional[torch.Tensor] = None
+
+    def attach(self, rt) -> None:
+        super().attach(rt)
+        i = torch.arange(self.n_rot // 2, dtype=torch.float64)
+        inv = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / max(self.n_rot, 1))
+        self.inv_freq = inv.to(torch.float32).to(rt.device)
+
+
 @register_position_encoding("none")
 class NoPosition(PositionEncoding):
     fused = True

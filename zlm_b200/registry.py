@@ -15,8 +15,8 @@ from typing import Any, Callable, Dict, Mapping, Type
 
 from .config.spec import ConfigError, ModelSpec
 
-# architecture name (config.json "architectures"[0]) -> configuration class with
-# from_dict(mapping) and to_model_spec()
+# architecture name (config.json "architectures"[0], or its "architecture" string) -> configuration
+# class with from_dict(mapping) and to_model_spec()
 ARCHITECTURES: Dict[str, Any] = {}
 
 # part registries: kind -> class
@@ -78,9 +78,14 @@ def lookup(table: Dict[str, Any], what: str, kind: str):
 
 
 def architecture_name(config: Mapping[str, Any]) -> str:
+    """The model class a config.json names: the first entry of its ``architectures`` list, or, for a
+    writer that names one design with a plain string, its ``architecture``."""
     archs = config.get("architectures")
+    if archs is None and isinstance(config.get("architecture"), str) and config["architecture"]:
+        return config["architecture"]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a list with the model class name")
+        raise ConfigError("config.json: 'architectures' must be a list with the model class name "
+                          "(or 'architecture' a string)")
     return archs[0]
 
 

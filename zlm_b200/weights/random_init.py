@@ -48,7 +48,7 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, device, dtype: torch.dt
         elif spec.init != "normal":
             raise ValueError(f"unknown init '{spec.init}' for {name}")
         out[b:e] = t.to(dtype)
-    return out.view(*spec.shape)
+    return out.reshape(tuple(spec.shape))
 
 
 def random_tensors(expected: Mapping[str, ParamSpec], seed: int, device="cpu",
