@@ -110,8 +110,19 @@ def route(h: torch.Tensor, w_router: torch.Tensor, top: int) -> Tuple[torch.Tens
     return idx, w
 
 
-def moe_ff(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str, mlp: Mapping[str, Any]) -> torch.Tensor:
+def route_margin(h: torch.Tensor, w_router: torch.Tensor, top: int) -> torch.Tensor:
+    """[T]: how far the last chosen expert's score lies above the best one not chosen (inf if all are chosen)."""
+    s = torch.sigmoid(h @ w_router.t()).sort(dim=-1, descending=True).values
+    if top >= s.shape[-1]:
+        return torch.full(s.shape[:1], math.inf, dtype=s.dtype)
+    return s[:, top - 1] - s[:, top]
+
+
+def moe_ff(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str, mlp: Mapping[str, Any],
+           margins: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
     idx, w = route(h, t[p + "router"], int(mlp["router"]["top"]))
+    if margins is not None:
+        margins.append(route_margin(h, t[p + "router"], int(mlp["router"]["top"])))
     out = torch.zeros_like(h)
     for i in range(h.shape[0]):
         for e, we in zip(idx[i].tolist(), w[i]):
@@ -123,8 +134,9 @@ def moe_ff(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str, mlp: Mapping[
 
 
 def forward(t: Mapping[str, torch.Tensor], cfg: Mapping[str, Any], ids: Sequence[int],
-            return_layers: bool = False):
-    """Logits [T, vocab] of one whole sequence (and the stream after every layer)."""
+            return_layers: bool = False, margins: Optional[List[torch.Tensor]] = None):
+    """Logits [T, vocab] of one whole sequence (and the stream after every layer).  ``margins`` collects,
+    per routed layer, every position's ``route_margin``."""
     eps = float(cfg["norm"]["eps"])
     ids = torch.as_tensor(list(ids), dtype=torch.long)
     pos = torch.arange(len(ids))
@@ -144,7 +156,7 @@ def forward(t: Mapping[str, torch.Tensor], cfg: Mapping[str, Any], ids: Sequence
         mlp = layer.get("mlp")
         if mlp is not None:
             h = scalar_norm(x, t[p + "norm2"], eps)
-            x = x + (dense_ff(h, t, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, t, p + "mlp.", mlp))
+            x = x + (dense_ff(h, t, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, t, p + "mlp.", mlp, margins))
         after.append(x)
     logits = scalar_norm(x, t["final.norm"], eps) @ t["head"].t()
     return (logits, torch.stack(after)) if return_layers else logits

@@ -76,6 +76,19 @@ static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16
     return rc;
 }
 
+// The combine step alone, for other split attention kernels that leave (max, sum, O) per split in the same
+// layout: part_o [T][nq][splits][hd], part_ml [T][nq][splits][2] (maxima in base-2 exponents).
+extern "C" int zlm_attention_decode_combine(void* out, int out_stride, const float* part_o, const float* part_ml,
+                                            const int* token_pos, int T, int nq, int hd, int splits, int per, int window,
+                                            cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(splits >= 1 && splits <= COMB_MAX_SPLITS && nq > 0 && nq <= 65535 && hd > 0 && per >= 1,
+                "attention_decode_combine: splits=%d heads=%d size=%d", splits, nq, hd);
+    zlm_launch(attention_decode_combine_kernel, dim3(T, nq), dim3(COMB_THREADS), 0, st, (__nv_bfloat16*)out, out_stride,
+               part_o, part_ml, token_pos, nq, hd, splits, per, window);
+    return zlm_check_launch("attention_decode_combine");
+}
+
 // 1 if this kernel takes the shape, 0 if the caller has to use the generic kernel
 extern "C" int zlm_attention_decode_supported(int nq, int nkv, int hd) {
     return (nkv > 0 && nq % nkv == 0 && nq / nkv <= 16 && hd % 16 == 0 && hd >= 16 && hd <= 128) ? 1 : 0;

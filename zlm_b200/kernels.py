@@ -698,15 +698,43 @@ class CudaKernels:
 
     def latent_attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
                          token_pos: torch.Tensor, token_slot: torch.Tensor, heads: int, kv_rank: int, rot_dim: int,
-                         scale: float, window: int = 0, plan=None, len_bucket: Optional[int] = None) -> None:
+                         scale: float, window: int = 0, plan=None, len_bucket: Optional[int] = None,
+                         impl: Optional[str] = None) -> None:
         """out[t, h, :kv_rank] = sum_j softmax_j(q[t, h] . rec_j * scale) rec_j[:kv_rank] over the records
         [start, pos[t]] of the token's slot in ``pool`` [pages, PAGE_TOKENS, kv_rank + rot_dim]: one
-        key/value record per token that every head reads (q [T, heads * (kv_rank + rot_dim)])."""
+        key/value record per token that every head reads (q [T, heads * (kv_rank + rot_dim)]).  ``plan`` is
+        the step's context: with it bf16 steps run on the tensor-core kernel where it takes the sizes (kv_rank
+        and rot_dim multiples of 16); without it, in 32-bit, or with ``impl="plain"``, the plain kernel runs."""
         T = q.shape[0]
         D = kv_rank + rot_dim
         assert q.shape[1] == heads * D and out.shape == (T, heads * kv_rank) and q.dtype == out.dtype == pool.dtype
         assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
         assert tuple(pool.shape[1:]) == (PAGE_TOKENS, D)
+        if (q.dtype == torch.bfloat16 and plan is not None and impl != "plain"
+                and self.lib.zlm_latent_attention_mma_supported(c_int(heads), c_int(kv_rank), c_int(rot_dim))
+                and q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0 and out.stride(0) % 2 == 0):
+            # the tensor-core kernel: a decode step cuts the sequences' pages into splits (all heads of a tile
+            # share one pass over the records: the head tiles stand where the other attention has kv heads);
+            # prompts and portions give a block several neighbouring tokens that share the staged pages
+            tiles = (heads + 15) // 16
+            if plan.is_decode:
+                if len_bucket is None:
+                    len_bucket = attention_len_bucket(plan.max_len)
+                splits, per = decode_splits(T, tiles, len_bucket, self.decode_blocks or self.sm_count * DECODE_BLOCKS_PER_SM)
+                qt, fresh = 1, max(1, int(getattr(plan, "max_new", 1) or 1))
+            else:
+                splits, per = 1, max(1, (int(plan.max_len) + PAGE_TOKENS - 1) // PAGE_TOKENS)
+                qt, fresh = int(self.lib.zlm_latent_attention_mma_tokens(c_int(kv_rank), c_int(rot_dim))), 0
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = plan.scratch("lat.part_o", (T * heads * splits * kv_rank,), torch.float32)
+                part_ml = plan.scratch("lat.part_ml", (T * heads * splits * 2,), torch.float32)
+            self._call("zlm_latent_attention_mma", self._p(out), c_int(out.stride(0)), self._p(q), c_int(q.stride(0)),
+                       self._p(pool), self._p(block_table), c_int(block_table.stride(0)), self._p(token_pos),
+                       self._p(token_slot), c_int(T), c_int(heads), c_int(kv_rank), c_int(rot_dim), c_float(scale),
+                       c_int(window), c_int(qt), c_int(splits), c_int(per), self._p(part_o), self._p(part_ml),
+                       c_int(fresh), self._stream())
+            return
         self._call("zlm_latent_attention", self._p(out), c_int(out.stride(0)), self._p(q), c_int(q.stride(0)),
                    c_int(_dt(q)), self._p(pool), self._p(block_table), c_int(block_table.stride(0)),
                    self._p(token_pos), self._p(token_slot), c_int(T), c_int(heads), c_int(kv_rank), c_int(rot_dim),

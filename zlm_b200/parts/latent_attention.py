@@ -68,6 +68,14 @@ class LatentAttention(Mixer):
         super().attach(rt)
         self.position.attach(rt)
 
+    def step_key(self, ctx: StepContext):
+        # the decode kernel cuts the longest sequence's pages into splits: its grid, and with it a
+        # captured step, holds for one rounded length
+        if not ctx.is_decode:
+            return None
+        from ..kernels import attention_len_bucket
+        return ("latent_attention", attention_len_bucket(ctx.max_len))
+
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         H, dn, dv, r = self.H, self.dn, self.dv, self.r
         w_q = params.pop("q")
@@ -116,8 +124,9 @@ class LatentAttention(Mixer):
         else:
             ql[:, :, :r].zero_()
         ol = rt.ws.get("lat.ol", (T, H * r), rt.dtype)
+        key = self.step_key(ctx)
         k.latent_attention(ol, ql.view(T, H * R), cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot,
-                           H, r, dr, self.scale, self.window, ctx)
+                           H, r, dr, self.scale, self.window, ctx, len_bucket=key[1] if key else None)
         ov = rt.ws.get("lat.ov", (T, H * dv), rt.dtype)
         k.head_linear(ov.view(T, H, dv), ol.view(T, H, r), self.w_uv)
         k.linear(residual, ov, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next

@@ -123,7 +123,7 @@ def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor],
         for name in order:
             t = tensors[name].detach().contiguous().cpu()
             if t.numel():
-                f.write(t.view(torch.uint8).reshape(-1).numpy().tobytes()
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes()
                         if t.dtype != torch.bool else t.to(torch.uint8).numpy().tobytes())
 
 
