@@ -499,6 +499,113 @@ def profile(args) -> int:
     return 0
 
 
+# ---- another design beside its closest existing model (--design) -------------------------------------
+# Layer sizes that resemble real latent-attention / routed-expert models (fewer layers and a smaller
+# vocabulary, so that a pair of engines is built in seconds), each with a Qwen3-dense twin of the same
+# width, head count, layer count and vocabulary whose feed-forward does as many multiply-adds per token as
+# the routed layer's active experts.
+def _nuvilorn(width, heads, dim, rot, vdim, rank, dense_ff, experts, top, ff, shared, layers, vocab):
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank,
+             "scale": (dim + rot) ** -0.5, "rot": {"base": 10000.0, "dims": rot}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": shared}}
+    return {"architecture": "Nuvilorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": "latent_attention", "mixer": dict(mixer),
+                        "mlp": {"kind": "dense", "ff": dense_ff} if i == 0 else moe} for i in range(layers)]}
+
+
+def _twin(width, heads, kv_heads, inter, layers, vocab):
+    return dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=kv_heads, head_dim=128, intermediate_size=inter, vocab_size=vocab)
+
+
+DESIGN_SIZES = {
+    # 16 heads of 128 + 64, latents of 512, 64 experts of 1408 (6 a token) and a shared one of 2816
+    "lite": (_nuvilorn(2048, 16, 128, 64, 128, 512, 10944, 64, 6, 1408, 2816, 6, 32768), _twin(2048, 16, 4, 7552, 6, 32768)),
+    # 8 heads of 64 + 32, latents of 256, 32 experts of 512 (4 a token) and a shared one of 1024
+    "small": (_nuvilorn(1024, 8, 64, 32, 64, 256, 4096, 32, 4, 512, 1024, 6, 32768), _twin(1024, 8, 4, 2048, 6, 32768)),
+    # 32 heads, width 4096, 32 experts of 2048 (2 a token) and a shared one of 2048
+    "wide": (_nuvilorn(4096, 32, 128, 64, 128, 512, 12288, 32, 2, 2048, 2048, 4, 32768), _twin(4096, 32, 8, 4096, 4, 32768)),
+}
+
+
+def design_comparison(args) -> int:
+    """Prefill of 2,048 tokens and decode at batch ``--batch`` from 2,048-token prompts, device-timed, for
+    the Nuvilorn design and for its Qwen3-dense twin at each of DESIGN_SIZES, with every operation of both
+    steps (CUDA events; decode operations as graphs of one step's calls); one JSON line."""
+    import torch
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.profiling import profile_engine
+    from zlm_b200.registry import config_from_dict
+    from zlm_b200.sampling import SamplingParams
+    pk = peaks()
+    greedy = SamplingParams()
+    B, L, steps, warmup = args.batch, PROMPT_LEN, min(args.steps, 64), max(3, args.warmup)
+    g = torch.Generator().manual_seed(0)
+    out = {"metric": "prefill and decode tokens/s of Nuvilorn beside Qwen3 dense at equal sizes", "unit": "tokens/s",
+           "dtype": "bf16", "data": "synthetic", "batch": B, "prompt_len": L, "peaks": pk, "sizes": {}}
+    for name in ([args.design_size] if args.design_size else list(DESIGN_SIZES)):
+        rec = {}
+        for which, d in zip(("nuvilorn", "qwen3_twin"), DESIGN_SIZES[name]):
+            cfg = config_from_dict(d)
+            eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=B * (L + 256),
+                                     max_batch=B, max_seq_len=L + 256, max_step_tokens=B * L)
+            ps = [torch.randint(0, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(B)]
+            times = []
+            for i in range(4):                           # a prefill step alone, the best of three after a warm-up
+                s = eng.new_sequence()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                time.sleep(0.2)
+                e0.record()
+                eng.step([StepEntry(s, ps[0], [L - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                if i:
+                    times.append(e0.elapsed_time(e1))
+                eng.release(s)
+            slots = [eng.new_sequence() for _ in ps]
+            first = []
+            for i in range(0, B, 4):
+                first += eng.prefill_sample(slots[i:i + 4], ps[i:i + 4], greedy, list(range(i, min(B, i + 4))))
+            dec = eng.decoder
+            dec.step(slots, first, greedy)
+            for _ in range(warmup):
+                dec.step(slots, None, greedy)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                dec.step(slots, None, greedy)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            for s in slots:
+                eng.release(s)
+            eng.check(sync=True)
+            r = {"prefill_tok_s": round(L / min(times) * 1e3, 1), "prefill_ms": round(min(times), 3),
+                 "decode_tok_s": round(B / ms * 1e3, 1), "decode_ms": round(ms, 4), "launches_per_step": dec.launches_per_step,
+                 "cache_bytes_per_token": eng.cache.bytes_per_token()}
+            if not args.no_kernels:
+                for phase, n in (("prefill", 1), ("decode", B)):
+                    rows = profile_engine(eng, ps[:n], decode_steps=0 if phase == "prefill" else 6)
+                    ops = {}
+                    for row in rows:
+                        if row["phase"] != phase or row["op"] in ("argmax", "sample", "embed"):
+                            continue
+                        f_b, f_f = row["gb_s"] / pk["hbm_gbs"], row["tflop_s"] / pk["bf16_tflops"]
+                        ops[row["op"]] = {"us": row["us_per_call"], "calls": row["calls"], "gb_s": row["gb_s"],
+                                          "tflop_s": row["tflop_s"], "frac": round(max(f_b, f_f), 3),
+                                          "bound": "hbm" if f_b >= f_f else "tensor"}
+                    r["kernels_" + phase] = ops
+            rec[which] = r
+            del eng, dec
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][name] = rec
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -523,6 +630,9 @@ def main() -> int:
     ap.add_argument("--no-kernels", action="store_true", help="leave out the per-operation times")
     ap.add_argument("--no-other-sizes", action="store_true",
                     help="leave out the Qwen3-0.6B and Qwen3-32B sizes that the default run adds under points")
+    ap.add_argument("--design", choices=["nuvilorn"],
+                    help="instead of the headline run: that design beside its Qwen3-dense twin at a few layer sizes")
+    ap.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None, help="with --design: one of the sizes only")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -536,6 +646,8 @@ def main() -> int:
         return profile(args)
     if args.unequal:
         return unequal(args)
+    if args.design:
+        return design_comparison(args)
     args.warmup = max(3, args.warmup)
     print(json.dumps(run(args)))
     return 0

@@ -136,8 +136,8 @@ def test_prep_norms_rotates_and_writes_records(dtype, H, dn, dr, r, n_rot):
 def test_per_head_products(dtype):
     k = K()
     g = torch.Generator().manual_seed(13)
-    for T, H, N, Kd in [(1, 3, 40, 16), (9, 2, 24, 8), (70, 18, 8, 72), (5, 1, 7, 33)]:
-        x = torch.randn(T, H, Kd + 5, generator=g).to(DT[dtype]).cuda()
+    for T, H, N, Kd in [(1, 3, 40, 16), (9, 2, 24, 8), (70, 18, 8, 72), (5, 1, 7, 33), (300, 3, 136, 64), (129, 2, 16, 264)]:
+        x = torch.randn(T, H, Kd + (8 if T > 100 else 5), generator=g).to(DT[dtype]).cuda()
         w = (torch.randn(H, N, Kd, generator=g) / Kd ** 0.5).to(DT[dtype]).cuda()
         out = torch.zeros(T, H, N + 3, dtype=DT[dtype], device="cuda")
         k.head_linear(out[:, :, 3:], x[:, :, :Kd], w)
@@ -347,3 +347,43 @@ def test_one_key_holds_the_weight_on_tensor_cores(decode, window):
             inside = not window or j > pos - window
             hit = (got[0].double().cpu() - rec[j, :r]).norm() / rec[j, :r].norm()
             assert (hit < 0.05) == inside, f"key {j} from {pos} window {window}: inside={inside}, distance {hit:.3f}"
+
+
+@pytest.mark.parametrize("T, E, top, F, W", [(17, 64, 1, 16, 64), (37, 5, 2, 32, 64), (300, 7, 3, 24, 72), (700, 4, 4, 136, 128),
+                                            (2048, 16, 2, 64, 256), (64, 64, 6, 16, 64)])
+def test_grouped_experts_equal_the_token_by_token_kernels(T, E, top, F, W):
+    """Steps of many tokens sort their (token, choice) pairs by expert and run tiles of rows: the same sums
+    as the kernels that stream an expert per pair, for few and many rows an expert, experts without any
+    row, and tiles that are not full."""
+    k = K()
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, W, generator=g).to(torch.bfloat16).cuda()
+    w_up = (torch.randn(E, F, W, generator=g) / W ** 0.5).to(torch.bfloat16).cuda()
+    w_down = (torch.randn(E, W, F, generator=g) / F ** 0.5).to(torch.bfloat16).cuda()
+    router = (torch.randn(E, W, generator=g) * 0.4).to(torch.bfloat16)
+    if E >= 16:
+        router[-3:] = 0.0
+        router[-3:, 0] = -50.0                 # three experts that no token chooses:
+        x[:, 0] = x[:, 0].abs() + 0.5          # their logit is -50 times a positive number
+    idx = torch.zeros(T, top, dtype=torch.int32, device="cuda")
+    wgt = torch.zeros(T, top, dtype=torch.float32, device="cuda")
+    k.moe_route(idx, wgt, x, router.cuda(), top)
+    if E >= 16:
+        assert int(idx.max()) < E - 3
+    act = torch.zeros(T, top, F, dtype=torch.bfloat16, device="cuda")
+    want = torch.zeros(T, W, device="cuda")
+    k.moe_up(act, x, w_up, idx, wgt)
+    k.moe_down(want, act, w_down, idx)
+    got = torch.zeros(T, W, device="cuda")
+    k.moe_grouped(got, x, w_up, w_down, idx, wgt)
+    # (the two kernels sum in different orders, and an activation on the edge between two bf16 values may
+    # fall either way)
+    err = (got - want).double().norm() / want.double().norm()
+    assert err < 3e-4, f"grouped experts T={T} E={E} top={top}: differs by {err:.3e} of its norm"
+    # and against the plain implementation
+    xs = x.double().cpu()
+    ref = torch.zeros(T, W, dtype=torch.float64)
+    for i in range(0, T, max(1, T // 40)):
+        for e, we in zip(idx[i].tolist(), wgt[i].double().cpu()):
+            ref[i] += P.relu2_expert(we * xs[i], w_up[e].double().cpu(), w_down[e].double().cpu())
+        close(got[i], ref[i], "bfloat16", f"grouped experts row {i}")

@@ -50,7 +50,7 @@ __device__ __forceinline__ bool rows_vectorise(const TA* a, const TA* b, int K, 
 }
 
 // ---------------------------------------------------------------------------- router
-#define ROUTE_WARPS 4
+#define ROUTE_WARPS 16
 // score_kind 0: sigmoid of each logit; 1: softmax over the experts.  renorm: the chosen weights divided by their sum.
 template <typename TA>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)

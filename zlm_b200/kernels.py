@@ -685,13 +685,20 @@ class CudaKernels:
                    c_int(block_table.stride(0) if dkv is not None else 0), self._p(pool if dkv is not None else None),
                    c_int(T), c_int(heads), c_int(dim), c_int(rot_dim), c_int(kv_rank), self._stream())
 
-    def head_linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
+    def head_linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, impl: Optional[str] = None) -> None:
         """out[t, h, :] = w[h] @ x[t, h, :] for per-head matrices w [heads, N, K]; x [T, heads, K] and out
         [T, heads, N] may be views with any token and head strides (innermost contiguous)."""
         T, H, K = x.shape
         N = w.shape[1]
         assert w.shape == (H, N, K) and w.is_contiguous() and out.shape == (T, H, N)
         assert x.dtype == w.dtype == out.dtype and x.stride(2) == 1 and out.stride(2) == 1
+        if (x.dtype == torch.bfloat16 and T > 16 and impl != "plain" and x.data_ptr() % 16 == 0
+                and self.lib.zlm_head_linear_mma_supported(c_int(K), c_int(x.stride(0)), c_int(x.stride(1)))):
+            # many tokens: tiles of tokens per head on the tensor cores
+            self._call("zlm_head_linear_mma", self._p(out), c_int(out.stride(0)), c_int(out.stride(1)), self._p(x),
+                       c_int(x.stride(0)), c_int(x.stride(1)), self._p(w), c_int(T), c_int(H), c_int(N), c_int(K),
+                       self._stream())
+            return
         self._call("zlm_head_linear", self._p(out), c_int(out.stride(0)), c_int(out.stride(1)), self._p(x),
                    c_int(x.stride(0)), c_int(x.stride(1)), self._p(w), c_int(_dt(x)), c_int(T), c_int(H), c_int(N),
                    c_int(K), self._stream())
@@ -779,6 +786,28 @@ class CudaKernels:
         assert stream.dtype == torch.float32 and stream.shape == (T, N) and stream.is_contiguous()
         self._call("zlm_moe_down", self._p(stream), self._p(act), self._p(w_down), self._p(idx), c_int(_dt(act)), c_int(T),
                    c_int(top), c_int(F), c_int(N), self._stream())
+
+    def moe_grouped(self, stream: torch.Tensor, x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                    idx: torch.Tensor, wgt: torch.Tensor, scale_input: bool = True) -> None:
+        """What ``moe_up`` and ``moe_down`` compute, for steps of many tokens (bf16): the (token, choice) pairs
+        are sorted by expert on the device and every expert's rows go through its matrices as tiles of one
+        grouped tensor-core product, so an expert's weights are read once per tile, not once per token."""
+        T, K = x.shape
+        E, F, _ = w_up.shape
+        top = idx.shape[1]
+        assert x.dtype == w_up.dtype == w_down.dtype == torch.bfloat16 and x.stride(1) == 1
+        assert w_up.shape == (E, F, K) and w_down.shape == (E, K, F) and w_up.is_contiguous() and w_down.is_contiguous()
+        assert stream.dtype == torch.float32 and stream.shape == (T, K) and stream.is_contiguous()
+        assert idx.shape == (T, top) and wgt.shape == (T, top) and idx.is_contiguous() and wgt.is_contiguous()
+        P = T * top
+        bm = int(self.lib.zlm_moe_grouped_tile_rows(c_int(P), c_int(E)))
+        tiles = int(self.lib.zlm_moe_grouped_max_tiles(c_int(P), c_int(E), c_int(bm)))
+        ints = self.scratch("moe.sorted", 2 * P + 3 * tiles, torch.int32, x.device)
+        act = self.scratch("moe.sorted_act", P * F, torch.bfloat16, x.device)
+        y = self.scratch("moe.sorted_out", P * K, torch.float32, x.device)
+        self._call("zlm_moe_grouped", self._p(stream), self._p(x), c_int(x.stride(0)), self._p(w_up), self._p(w_down),
+                   self._p(idx), self._p(wgt), c_int(T), c_int(top), c_int(E), c_int(F), c_int(K),
+                   c_int(1 if scale_input else 0), self._p(ints), self._p(act), self._p(y), self._stream())
 
     def relu2_scale(self, out: torch.Tensor, u: torch.Tensor, row_scale: Optional[torch.Tensor] = None) -> None:
         """out[t, i] = relu(u[t, i])^2 * row_scale[t]."""

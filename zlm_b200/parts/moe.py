@@ -87,9 +87,14 @@ class RoutedExperts(FeedForward):
         wgt = rt.ws.get("moe.wgt", (T, self.top), torch.float32)
         gate = rt.ws.get("moe.gate", (T,), torch.float32) if self.shared_gate else None
         k.moe_route(idx, wgt, x, self.w_router, self.top, gate, self.w_sg, self.score, self.renormalize)
-        act = rt.ws.get("moe.act", (T, self.top, self.F), rt.dtype)
-        k.moe_up(act, x, self.w_up, idx, wgt, self.scale_input)
-        k.moe_down(residual, act, self.w_down, idx)
+        if T > 16 and rt.dtype == torch.bfloat16 and self.F % 8 == 0 and self.hidden % 8 == 0 and hasattr(k, "moe_grouped"):
+            # many tokens: pairs sorted by expert, each expert's rows as tiles of one grouped product
+            k.moe_grouped(residual, x, self.w_up, self.w_down, idx, wgt, self.scale_input)
+        else:
+            # few tokens (and the 32-bit path): every (token, choice) streams its expert's matrices
+            act = rt.ws.get("moe.act", (T, self.top, self.F), rt.dtype)
+            k.moe_up(act, x, self.w_up, idx, wgt, self.scale_input)
+            k.moe_down(residual, act, self.w_down, idx)
         if self.SF:
             u = rt.ws.get("moe.shared_u", (T, self.SF), rt.dtype)
             k.linear(u, x, self.w_sup)

@@ -196,6 +196,59 @@ class ProfilingKernels:
         return self._timed(kind, n, 4.0 * nq * hd * pairs, self.k.attention, out, q, pool, block_table, token_pos,
                            token_slot, nq, nkv, hd, scale, window, plan, len_bucket=len_bucket)
 
+    # latent attention and routed experts
+    def latent_prep(self, q, q_rot, dkv, *args, **kw):
+        n = _nbytes(q) + _nbytes(q_rot) + 2 * _nbytes(dkv)
+        return self._timed("latent norm+rope+cache_write", n, 0, self.k.latent_prep, q, q_rot, dkv, *args, **kw)
+
+    def head_linear(self, out, x, w):
+        T = x.shape[0]
+        n = _nbytes(w) + T * x.shape[1] * x.shape[2] * x.element_size() + T * out.shape[1] * out.shape[2] * out.element_size()
+        return self._timed(f"per-head linear [{w.shape[1]}x{w.shape[2]}]", n, 2.0 * T * w.numel(), self.k.head_linear, out, x, w)
+
+    def latent_attention(self, out, q, pool, block_table, token_pos, token_slot, heads, kv_rank, rot_dim, scale,
+                         window=0, plan=None, len_bucket=None, impl=None):
+        keys_read, pairs = 0, 0
+        if plan is not None and getattr(plan, "h_seq_start", None):
+            for start, new in zip(plan.h_seq_start, plan.h_seq_new):
+                end = start + new
+                keys_read += end - (max(0, start + 1 - window) if window else 0)
+                for p in range(start, end):
+                    pairs += (p + 1) - (max(0, p + 1 - window) if window else 0)
+        n = _nbytes(q) + _nbytes(out) + keys_read * (kv_rank + rot_dim) * pool.element_size()
+        kind = "latent attention decode" if (plan is not None and plan.is_decode) else "latent attention prefill"
+        return self._timed(kind, n, 2.0 * heads * (2 * kv_rank + rot_dim) * pairs, self.k.latent_attention, out, q, pool,
+                           block_table, token_pos, token_slot, heads, kv_rank, rot_dim, scale, window, plan,
+                           len_bucket=len_bucket, impl=impl)
+
+    def moe_route(self, idx, wgt, x, w_router, top, *args, **kw):
+        T, K = x.shape
+        return self._timed("router", _nbytes(w_router) + T * K * x.element_size(), 2.0 * T * w_router.numel(),
+                           self.k.moe_route, idx, wgt, x, w_router, top, *args, **kw)
+
+    def _experts_read(self, T, top, w):
+        return min(T * top, w.shape[0]) * w.shape[1] * w.shape[2] * w.element_size()
+
+    def moe_up(self, act, x, w_up, idx, wgt, scale_input=True):
+        T, top = idx.shape
+        return self._timed("experts up", self._experts_read(T, top, w_up) + _nbytes(act), 2.0 * T * top * w_up.shape[1] * w_up.shape[2],
+                           self.k.moe_up, act, x, w_up, idx, wgt, scale_input)
+
+    def moe_down(self, stream, act, w_down, idx):
+        T, top = idx.shape
+        return self._timed("experts down", self._experts_read(T, top, w_down) + _nbytes(act) + 2 * _nbytes(stream),
+                           2.0 * T * top * w_down.shape[1] * w_down.shape[2], self.k.moe_down, stream, act, w_down, idx)
+
+    def moe_grouped(self, stream, x, w_up, w_down, idx, wgt, scale_input=True):
+        T, top = idx.shape
+        n = self._experts_read(T, top, w_up) + self._experts_read(T, top, w_down) + 2 * _nbytes(stream) + T * top * (
+            4 * w_up.shape[1] + 8 * w_down.shape[1] + 2 * x.shape[1])
+        return self._timed("experts (sorted, grouped up+down)", n, 4.0 * T * top * w_up.shape[1] * w_up.shape[2],
+                           self.k.moe_grouped, stream, x, w_up, w_down, idx, wgt, scale_input)
+
+    def relu2_scale(self, out, u, row_scale=None):
+        return self._timed("relu2*gate", _nbytes(out) + _nbytes(u), 0, self.k.relu2_scale, out, u, row_scale)
+
     def argmax(self, out, logits, fresh=False):
         return self._timed("argmax", _nbytes(logits), 0, self.k.argmax, out, logits, fresh=fresh)
 
