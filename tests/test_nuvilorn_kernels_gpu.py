@@ -375,11 +375,19 @@ def test_grouped_experts_equal_the_token_by_token_kernels(T, E, top, F, W):
     k.moe_up(act, x, w_up, idx, wgt)
     k.moe_down(want, act, w_down, idx)
     got = torch.zeros(T, W, device="cuda")
-    k.moe_grouped(got, x, w_up, w_down, idx, wgt)
+    k.moe_grouped(got, x, w_up, w_down, idx, wgt, impl="mma")
     # (the two kernels sum in different orders, and an activation on the edge between two bf16 values may
     # fall either way)
     err = (got - want).double().norm() / want.double().norm()
     assert err < 3e-4, f"grouped experts T={T} E={E} top={top}: differs by {err:.3e} of its norm"
+    # the tcgen05 form: the weight is multiplied into the bf16 input rows, so it differs by their rounding
+    got_tc = torch.zeros(T, W, device="cuda")
+    k.moe_grouped(got_tc, x, w_up, w_down, idx, wgt, impl="tc")
+    k.check_status(sync=True)
+    err = (got_tc - want).double().norm() / want.double().norm()
+    assert err < 1e-2, f"grouped experts on tcgen05 T={T} E={E} top={top}: differs by {err:.3e} of its norm"
+    rows = (got_tc - want).double().norm(dim=1) / want.double().norm(dim=1).clamp_min(1e-9)
+    assert float(rows.max()) < 5e-2, f"grouped experts on tcgen05: token {int(rows.argmax())} differs by {rows.max():.3e}"
     # and against the plain implementation
     xs = x.double().cpu()
     ref = torch.zeros(T, W, dtype=torch.float64)

@@ -36,6 +36,17 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f 
 // a thread's 16 consecutive outputs (columns n .. n+15) of token `row` in the wanted mode
 template <int MODE>
 __device__ __forceinline__ void store_row16(const float* v, void* Y, int row, int n, int T, int N, int ldy) {
+    if (MODE == 6) {
+        // relu(z)^2, stored as bf16
+        float r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float z = fmaxf(v[i], 0.f);
+            r[i] = z * z;
+        }
+        store_row16<0>(r, Y, row, n, T, N, ldy);
+        return;
+    }
     if (row >= T || n >= N) return;
     const bool whole = n + 16 <= N;
 #ifdef ZLM_BOUNDS_CHECK
@@ -300,7 +311,12 @@ static int tile_group(int bm, int K) {
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                          void* __restrict__ Y, int T, int N, int K, int ldy, int gm) {
+                          void* __restrict__ Y, int T, int N, int K, int ldy, int gm,
+                          const int* __restrict__ m_tile_group, int group_rows) {
+    // A grouped product (m_tile_group given): token tile tm multiplies the matrix of group m_tile_group[tm],
+    // whose N rows start at row group * group_rows of the second operand; tiles of group -1 are not needed in
+    // this step and every role passes over them.  The table is written by a kernel of the same step and is
+    // read after the wait for it.
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -343,7 +359,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
                 int tm, tn;
                 tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
-                const int a0row = tm * TC_BM, b0row = tn * BN;
+                int group = 0;
+                if (m_tile_group) {
+                    group = m_tile_group[tm];
+                    if (group < 0) continue;
+                }
+                const int a0row = tm * TC_BM, b0row = group * group_rows + tn * BN;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
@@ -364,7 +385,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                                    ((unsigned)(TC_BM >> 4) << 24);
             unsigned it = 0, local = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                if (m_tile_group) {
+                    int tm, tn;
+                    tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
+                    if (m_tile_group[tm] < 0) continue;
+                }
                 const unsigned buf = local & 1;
                 // the epilogue must have drained this accumulator (two tiles ago)
                 ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag, 4);
@@ -382,16 +408,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     tc_commit(&empty[s]);
                 }
                 tc_commit(&acc_full[buf]);
+                ++local;
             }
             if (!ok) { tc_commit(&acc_full[0]); tc_commit(&acc_full[1]); }     // let the epilogue out
         }
     } else {
         const int lg = warp & 3;
         unsigned local = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
             const unsigned buf = local & 1;
             int tm, tn;
             tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
+            if (m_tile_group && m_tile_group[tm] < 0) continue;
             const int a0row = tm * TC_BM, b0row = tn * BN;
             const bool ok = mbar_wait_warp(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
             tc_fence_after();
@@ -406,6 +434,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);      // one arrival per epilogue warp
+            ++local;
         }
     }
     tc_fence_before();
@@ -1155,7 +1184,8 @@ static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, in
             }                                                                                              \
             attr_set = true;                                                                               \
         }                                                                                                  \
-        zlm_launch(kern, dim3(blocks), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy, tile_group(TC_BM, K)); \
+        zlm_launch(kern, dim3(blocks), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy, tile_group(TC_BM, K), \
+                   (const int*)nullptr, 0); \
     }
     if (mode == 0) ZLM_TCP_LAUNCH(0)
     else if (mode == 1) ZLM_TCP_LAUNCH(1)
@@ -1279,6 +1309,51 @@ static int launch_tc_few(void* Y, const void* X, const void* W, int T, int N, in
     rc = zlm_check_launch("gemm_tc_few");
     if (rc || plan.ks <= 1) return rc;
     return launch_reduce(Y, scratch, T, N, ldy, mode, plan.ks, plan.whole / plan.t_tiles * TC_BM, st);
+}
+
+// A grouped product for routed experts: the rows of X come in tiles of 128, tile tm belongs to group
+// tile_group[tm] (-1: not used in this step), and multiplies that group's matrix, rows
+// [group * N, group * N + N) of W [groups * N, K]; Y [m_tiles * 128, N]; group_of_tile[tm] is tile tm's group.  The persistent single-block
+// form with its tiles' second operand looked up per token tile.
+// mode 0: Y bf16; mode 2: Y fp32; mode 6: Y bf16 = relu(.)^2.
+extern "C" int zlm_gemm_tc_grouped(void* Y, const void* X, const void* W, const int* group_of_tile, int m_tiles, int groups,
+                                   int N, int K, int ldy, int mode, cudaStream_t st) {
+    if (m_tiles == 0 || N == 0) return ZLM_OK;
+    const int T = m_tiles * TC_BM;
+    ZLM_REQUIRE(m_tiles > 0 && groups > 0 && N >= 8 && K >= 8 && K % 8 == 0, "gemm_tc_grouped: tiles=%d groups=%d N=%d K=%d",
+                m_tiles, groups, N, K);
+    ZLM_REQUIRE((long long)groups * N < (1ll << 31), "gemm_tc_grouped: %d groups of %d rows", groups, N);
+    ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && group_of_tile, "gemm_tc_grouped: operands must be 16-byte aligned");
+    ZLM_REQUIRE(mode == 0 || mode == 2 || mode == 6, "gemm_tc_grouped: mode %d", mode);
+    constexpr int BN = 256, STAGES = 4;
+    CUtensorMap mx, mw;
+    int rc = make_map(&mx, X, T, K, K, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mw, W, groups * N, K, K, BN);
+    if (rc) return rc;
+    const size_t smem = (size_t)STAGES * (TC_BM + BN) * TC_BK * 2 + 1024 + 256;
+    const long long tiles = (long long)m_tiles * ((N + BN - 1) / BN);
+    const int blocks = (int)(tiles < sm_count() ? tiles : sm_count());
+#define ZLM_TCG_LAUNCH(M)                                                                                  \
+    {                                                                                                      \
+        auto kern = gemm_tc_persistent_kernel<BN, STAGES, M>;                                              \
+        static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];              \
+        if (!attr_set) {                                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) {                                                                        \
+                zlm_set_error("gemm_tc_grouped: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
+                return ZLM_ERR_CUDA;                                                                       \
+            }                                                                                              \
+            attr_set = true;                                                                               \
+        }                                                                                                  \
+        zlm_launch(kern, dim3(blocks), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy, tile_group(TC_BM, K), \
+                   group_of_tile, N);                                                                       \
+    }
+    if (mode == 0) ZLM_TCG_LAUNCH(0)
+    else if (mode == 2) ZLM_TCG_LAUNCH(2)
+    else ZLM_TCG_LAUNCH(6)
+#undef ZLM_TCG_LAUNCH
+    return zlm_check_launch("gemm_tc_grouped");
 }
 
 // 1 if the tensor-memory kernel takes this product (else use zlm_gemm_bf16_mma)

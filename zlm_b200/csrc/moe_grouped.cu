@@ -27,7 +27,7 @@ __device__ __forceinline__ void mg_cp_async16(void* smem, const void* gmem, bool
 // One block.  counts and cursors in shared memory (E entries each); tile table: tile -> (expert, first
 // sorted row, rows), expert -1 for the tiles a step does not need.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles, int* __restrict__ perm,
+moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles, int padded, int* __restrict__ perm,
                 int* __restrict__ inv, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                 int* __restrict__ tile_rows) {
     extern __shared__ int sh[];
@@ -37,6 +37,10 @@ moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles
     pdl_trigger();
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     pdl_wait();
+    // padded: every expert's rows start at a tile's first row, and the rows between are marked empty
+    if (padded)
+        for (int i = threadIdx.x; i < max_tiles * BM; i += blockDim.x)
+            if (ZLM_CHK(perm + i, 4)) perm[i] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < P; i += blockDim.x)
         if (ZLM_CHK(idx + i, 4)) atomicAdd(&count[min(max(idx[i], 0), E - 1)], 1);
@@ -44,12 +48,12 @@ moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles
     if (threadIdx.x == 0) {
         int s = 0, t = 0;
         for (int e = 0; e < E; ++e) {
-            start[e] = s;
+            start[e] = padded ? t * BM : s;
             tstart[e] = t;
             s += count[e];
             t += (count[e] + BM - 1) / BM;
         }
-        start[E] = s;
+        start[E] = padded ? t * BM : s;
         tstart[E] = t;
     }
     __syncthreads();
@@ -224,7 +228,8 @@ moe_grouped_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ A, co
 
 // stream[t, :] += sum_j y[inv[t * top + j], :]; one block per token
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(float* __restrict__ stream, const float* __restrict__ y, const int* __restrict__ inv, int top, int N) {
+moe_combine_kernel(float* __restrict__ stream, const float* __restrict__ y, const int* __restrict__ inv,
+                   const float* __restrict__ wgt, int top, int N) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -232,7 +237,7 @@ moe_combine_kernel(float* __restrict__ stream, const float* __restrict__ y, cons
         float sum = 0.f;
         for (int j = 0; j < top; ++j)
             if (ZLM_CHK(inv + (size_t)t * top + j, 4) && ZLM_CHK(y + (size_t)inv[(size_t)t * top + j] * N + n, 4))
-                sum += y[(size_t)inv[(size_t)t * top + j] * N + n];
+                sum += y[(size_t)inv[(size_t)t * top + j] * N + n] * (wgt ? wgt[(size_t)t * top + j] : 1.0f);
         if (ZLM_CHK(stream + (size_t)t * N + n, 4)) stream[(size_t)t * N + n] += sum;
     }
 }
@@ -322,7 +327,7 @@ extern "C" int zlm_moe_grouped(float* stream, const void* x, int x_stride, const
     int* perm = ints;
     int* inv = ints + P;
     int* tiles = ints + 2 * P;
-    zlm_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(3 * E + 2) * sizeof(int), st, idx, P, E, BM, max_tiles, perm,
+    zlm_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(3 * E + 2) * sizeof(int), st, idx, P, E, BM, max_tiles, 0, perm,
                inv, tiles, tiles + max_tiles, tiles + 2 * max_tiles);
     int rc = zlm_check_launch("moe_sort");
     if (rc) return rc;
@@ -339,7 +344,69 @@ extern "C" int zlm_moe_grouped(float* stream, const void* x, int x_stride, const
     else if (BM == 64) ZLM_MG(64, 2, 4);
     else ZLM_MG(128, 2, 4);
 #undef ZLM_MG
-    zlm_launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, stream, (const float*)y, (const int*)inv, top, K);
+    zlm_launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, stream, (const float*)y, (const int*)inv, (const float*)nullptr, top, K);
+    return zlm_check_launch("moe_combine");
+}
+
+// ---------------------------------------------------------------------------- the pieces, for the tcgen05 grouped product
+// Rows in tiles of 128 with every expert's rows starting at a tile (padded): ints = perm [max_tiles * 128] (-1: an
+// empty row) | inv [P] | tile table [3 * max_tiles]; the table's first part is what zlm_gemm_tc_grouped reads.
+extern "C" int zlm_moe_sort_padded(const int* idx, int P, int E, int max_tiles, int* ints, cudaStream_t st) {
+    ZLM_REQUIRE(P > 0 && E > 0 && E <= 2048 && max_tiles > 0, "moe_sort: pairs=%d experts=%d tiles=%d", P, E, max_tiles);
+    int* perm = ints;
+    int* inv = ints + (size_t)max_tiles * 128;
+    int* tiles = inv + P;
+    zlm_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(3 * E + 2) * sizeof(int), st, idx, P, E, 128, max_tiles, 1, perm,
+               inv, tiles, tiles + max_tiles, tiles + 2 * max_tiles);
+    return zlm_check_launch("moe_sort");
+}
+
+// xs[row, :] = bf16(w * x[token(row), :]) for the sorted, padded rows (zeros in empty rows); w the pair's weight
+// if scale (the weight on the expert's input), else 1
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(__nv_bfloat16* __restrict__ xs, const __nv_bfloat16* __restrict__ x, int x_stride,
+                  const int* __restrict__ perm, const float* __restrict__ wgt, int top, int K, int scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    if (!ZLM_CHK(perm + row, 4)) return;
+    const int pair = perm[row];
+    __nv_bfloat16* dst = xs + (size_t)row * K;
+    if (pair < 0) {
+        for (int c = threadIdx.x; c < K / 8; c += blockDim.x)
+            if (ZLM_CHK(dst + c * 8, 16)) *(uint4*)(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const __nv_bfloat16* src = x + (size_t)(pair / top) * x_stride;
+    const float w = (scale && ZLM_CHK(wgt + pair, 4)) ? wgt[pair] : 1.0f;
+    for (int c = threadIdx.x; c < K / 8; c += blockDim.x) {
+        if (!ZLM_CHK(src + c * 8, 16) || !ZLM_CHK(dst + c * 8, 16)) continue;
+        uint4 v = *(const uint4*)(src + c * 8);
+        if (scale) {
+            unsigned* u = (unsigned*)&v;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                u[i] = pack_bf16(__uint_as_float(u[i] << 16) * w, __uint_as_float(u[i] & 0xffff0000u) * w);
+        }
+        *(uint4*)(dst + c * 8) = v;
+    }
+}
+
+extern "C" int zlm_moe_gather(void* xs, const void* x, int x_stride, const int* perm, const float* wgt, int rows, int top,
+                              int K, int scale, cudaStream_t st) {
+    if (rows == 0) return ZLM_OK;
+    ZLM_REQUIRE(K % 8 == 0 && x_stride % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)xs % 16 == 0,
+                "moe_gather: K=%d and the row stride must be multiples of 8, operands 16-byte aligned", K);
+    zlm_launch(moe_gather_kernel, dim3(rows), dim3(256), 0, st, (__nv_bfloat16*)xs, (const __nv_bfloat16*)x, x_stride, perm, wgt,
+               top, K, scale);
+    return zlm_check_launch("moe_gather");
+}
+
+// stream[t, :] += sum_j (wgt[t, j] or 1) * y[inv[t, j], :]
+extern "C" int zlm_moe_combine(float* stream, const float* y, const int* inv, const float* wgt, int T, int top, int N,
+                               cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    zlm_launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, stream, y, inv, wgt, top, N);
     return zlm_check_launch("moe_combine");
 }
 

@@ -788,10 +788,12 @@ class CudaKernels:
                    c_int(top), c_int(F), c_int(N), self._stream())
 
     def moe_grouped(self, stream: torch.Tensor, x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
-                    idx: torch.Tensor, wgt: torch.Tensor, scale_input: bool = True) -> None:
+                    idx: torch.Tensor, wgt: torch.Tensor, scale_input: bool = True, impl: Optional[str] = None) -> None:
         """What ``moe_up`` and ``moe_down`` compute, for steps of many tokens (bf16): the (token, choice) pairs
         are sorted by expert on the device and every expert's rows go through its matrices as tiles of one
-        grouped tensor-core product, so an expert's weights are read once per tile, not once per token."""
+        grouped tensor-core product, so an expert's weights are read once per tile, not once per token.  Two
+        forms (``impl`` forces one): "tc", TMA + tcgen05 on tiles of 128 rows, where an expert gets about half
+        a tile or more; "mma", mma.sync on tiles of 16 to 128 rows, for fewer rows an expert."""
         T, K = x.shape
         E, F, _ = w_up.shape
         top = idx.shape[1]
@@ -800,6 +802,30 @@ class CudaKernels:
         assert stream.dtype == torch.float32 and stream.shape == (T, K) and stream.is_contiguous()
         assert idx.shape == (T, top) and wgt.shape == (T, top) and idx.is_contiguous() and wgt.is_contiguous()
         P = T * top
+        if impl is None:
+            # rows an expert gets on average: from about half a tile of 128 on, the tcgen05 grouped product
+            impl = "tc" if (P >= 64 * E and K % 8 == 0 and F % 8 == 0 and x.stride(0) % 8 == 0) else "mma"
+        if impl == "tc":
+            # pairs sorted into tiles of 128 rows that start at an expert's first row; the inputs gathered (with the
+            # pair's weight, which scales the expert's input) into that order; both products as grouped tcgen05
+            # products that look up each token tile's expert; the choices' rows added into the stream in order
+            tiles = (P + 127) // 128 + min(E, P)
+            rows = tiles * 128
+            ints = self.scratch("moe.padded", rows + P + 3 * tiles, torch.int32, x.device)
+            xs = self.scratch("moe.padded_x", rows * K, torch.bfloat16, x.device)
+            act = self.scratch("moe.padded_act", rows * F, torch.bfloat16, x.device)
+            y = self.scratch("moe.padded_out", rows * K, torch.float32, x.device)
+            perm, inv, table = ints[:rows], ints[rows:rows + P], ints[rows + P:]
+            self._call("zlm_moe_sort_padded", self._p(idx), c_int(P), c_int(E), c_int(tiles), self._p(ints), self._stream())
+            self._call("zlm_moe_gather", self._p(xs), self._p(x), c_int(x.stride(0)), self._p(perm), self._p(wgt), c_int(rows),
+                       c_int(top), c_int(K), c_int(1 if scale_input else 0), self._stream())
+            self._call("zlm_gemm_tc_grouped", self._p(act), self._p(xs), self._p(w_up), self._p(table), c_int(tiles), c_int(E),
+                       c_int(F), c_int(K), c_int(F), c_int(6), self._stream())
+            self._call("zlm_gemm_tc_grouped", self._p(y), self._p(act), self._p(w_down), self._p(table), c_int(tiles), c_int(E),
+                       c_int(K), c_int(F), c_int(K), c_int(2), self._stream())
+            self._call("zlm_moe_combine", self._p(stream), self._p(y), self._p(inv), self._p(None if scale_input else wgt),
+                       c_int(T), c_int(top), c_int(K), self._stream())
+            return
         bm = int(self.lib.zlm_moe_grouped_tile_rows(c_int(P), c_int(E)))
         tiles = int(self.lib.zlm_moe_grouped_max_tiles(c_int(P), c_int(E), c_int(bm)))
         ints = self.scratch("moe.sorted", 2 * P + 3 * tiles, torch.int32, x.device)

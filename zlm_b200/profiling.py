@@ -239,12 +239,12 @@ class ProfilingKernels:
         return self._timed("experts down", self._experts_read(T, top, w_down) + _nbytes(act) + 2 * _nbytes(stream),
                            2.0 * T * top * w_down.shape[1] * w_down.shape[2], self.k.moe_down, stream, act, w_down, idx)
 
-    def moe_grouped(self, stream, x, w_up, w_down, idx, wgt, scale_input=True):
+    def moe_grouped(self, stream, x, w_up, w_down, idx, wgt, scale_input=True, impl=None):
         T, top = idx.shape
         n = self._experts_read(T, top, w_up) + self._experts_read(T, top, w_down) + 2 * _nbytes(stream) + T * top * (
             4 * w_up.shape[1] + 8 * w_down.shape[1] + 2 * x.shape[1])
         return self._timed("experts (sorted, grouped up+down)", n, 4.0 * T * top * w_up.shape[1] * w_up.shape[2],
-                           self.k.moe_grouped, stream, x, w_up, w_down, idx, wgt, scale_input)
+                           self.k.moe_grouped, stream, x, w_up, w_down, idx, wgt, scale_input, impl=impl)
 
     def relu2_scale(self, out, u, row_scale=None):
         return self._timed("relu2*gate", _nbytes(out) + _nbytes(u), 0, self.k.relu2_scale, out, u, row_scale)
