@@ -119,3 +119,19 @@ def test_decode_attention_cut_always_covers_the_pages():
                     assert per >= 1 and 1 <= splits <= 1024, (rows, nkv, pages, blocks, splits, per)
                     assert splits * per >= pages, (rows, nkv, pages, blocks, splits, per)
                     assert (splits - 1) * per < pages, (rows, nkv, pages, blocks, splits, per)
+
+
+def test_latent_decode_splits_cover_the_pages():
+    """The latent attention's cut of a decode step: splits x pages per split cover the longest sequence for
+    every batch, head-tile count, length and wave, with at most 1024 splits, and one wave where that is possible."""
+    from zlm_b200.kernels import latent_decode_splits
+    for rows in (1, 2, 8, 17, 64, 300):
+        for tiles in (1, 2, 8):
+            for bucket in (1, 2, 3, 8, 32, 64, 512, 4096):
+                for wave in (8, 148, 444, 2000):
+                    splits, per = latent_decode_splits(rows, tiles, bucket, wave)
+                    assert splits * per >= bucket and (splits - 1) * per < bucket and 1 <= splits <= 1024
+                    if bucket >= 2 and splits <= 512:
+                        assert per >= 2
+                    if bucket * rows * tiles > 2 * wave and splits < 1024:
+                        assert splits * rows * tiles <= wave + rows * tiles

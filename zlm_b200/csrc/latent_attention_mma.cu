@@ -38,7 +38,9 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int grp = warp >> 2, wq = warp & 3, gtid = tid & (LM_GROUP - 1);
     const int g = lane >> 2, qd = lane & 3;
-    const int t0 = blockIdx.x * QT, htile = blockIdx.y, split = blockIdx.z;
+    // prompts: the last tokens of a sequence walk the most pages, so their blocks go first (blocks start in
+    // the order of their index) and the short ones fill in behind them
+    const int t0 = (QT > 1 ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x) * QT, htile = blockIdx.y, split = blockIdx.z;
     const GroupSync gsync{1 + grp, LM_GROUP};
     pdl_launch_dependents();
 
@@ -145,14 +147,37 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
                 const int mi = lane >> 3;
                 const int a_row = (lane & 7) + (mi & 1) * 8, a_chunk = mi >> 1;
                 const int b_row = wq * 16 + (mi >> 1) * 8 + (lane & 7), b_chunk = mi & 1;
-#pragma unroll 4
-                for (int ks = 0; ks < KS; ++ks) {
+                // (two chains of sums, even and odd steps of 16 columns: a product waits for the one before it
+                // in its chain, and D / 16 steps in one chain are most of a page's time)
+                float s2[2][4];
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s2[i][e] = 0.f;
+#pragma unroll 2
+                for (int ks = 0; ks + 1 < KS; ks += 2) {
+                    unsigned a[4], c[4], b00, b01, b10, b11, d00, d01, d10, d11;
+                    dec_ldsm4(a[0], a[1], a[2], a[3], qt + a_row * DS + (ks * 2 + a_chunk) * 8);
+                    dec_ldsm4(b00, b01, b10, b11, rt + b_row * DS + (ks * 2 + b_chunk) * 8);
+                    dec_ldsm4(c[0], c[1], c[2], c[3], qt + a_row * DS + (ks * 2 + 2 + a_chunk) * 8);
+                    dec_ldsm4(d00, d01, d10, d11, rt + b_row * DS + (ks * 2 + 2 + b_chunk) * 8);
+                    dec_mma(s[0], a, b00, b01);
+                    dec_mma(s[1], a, b10, b11);
+                    dec_mma(s2[0], c, d00, d01);
+                    dec_mma(s2[1], c, d10, d11);
+                }
+                if (KS & 1) {
+                    const int ks = KS - 1;
                     unsigned a[4], b00, b01, b10, b11;
                     dec_ldsm4(a[0], a[1], a[2], a[3], qt + a_row * DS + (ks * 2 + a_chunk) * 8);
                     dec_ldsm4(b00, b01, b10, b11, rt + b_row * DS + (ks * 2 + b_chunk) * 8);
                     dec_mma(s[0], a, b00, b01);
                     dec_mma(s[1], a, b10, b11);
                 }
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[i][e] += s2[i][e];
                 const int kbase = p * ZLM_PAGE + wq * 16;
                 float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -294,6 +319,13 @@ static size_t latent_mma_smem(int D, int QT) {
 // 1 if the tensor-core kernel takes the shape (else the caller uses the plain kernel)
 extern "C" int zlm_latent_attention_mma_supported(int H, int r, int dr) {
     return (H > 0 && r >= 16 && r % 16 == 0 && dr % 16 == 0 && r <= 512 && latent_mma_smem(r + dr, 1) <= 220 * 1024) ? 1 : 0;
+}
+
+// blocks of the one-token form that an SM holds at a time (its pages of records are large: shared memory decides)
+extern "C" int zlm_latent_attention_mma_blocks_per_sm(int r, int dr) {
+    const size_t one = latent_mma_smem(r + dr, 1) + 1024;
+    const int n = (int)((size_t)228 * 1024 / one);
+    return n < 1 ? 1 : (n > 8 ? 8 : n);
 }
 
 // tokens a block takes in a step of many tokens per sequence: as many as the shared memory holds

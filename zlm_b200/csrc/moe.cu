@@ -50,34 +50,71 @@ __device__ __forceinline__ bool rows_vectorise(const TA* a, const TA* b, int K, 
 }
 
 // ---------------------------------------------------------------------------- router
-#define ROUTE_WARPS 16
-// score_kind 0: sigmoid of each logit; 1: softmax over the experts.  renorm: the chosen weights divided by their sum.
-template <typename TA>
+#define ROUTE_WARPS 32
+// TOK tokens a block: a warp computes one expert's logit for all of them from one pass over the expert's row
+// (steps of many tokens would otherwise read the router's matrix once per token from L2); then warp j chooses
+// for token j.  score_kind 0: sigmoid of each logit; 1: softmax over the experts.  renorm: the chosen weights
+// divided by their sum.
+template <typename TA, int TOK>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restrict__ gate, const TA* __restrict__ x,
-                 int x_stride, const TA* __restrict__ Wr, const TA* __restrict__ wg, int E, int K, int top,
+                 int x_stride, const TA* __restrict__ Wr, const TA* __restrict__ wg, int T, int E, int K, int top,
                  int score_kind, int renorm) {
-    extern __shared__ float sc[];           // [E]
+    extern __shared__ float sc_all[];           // [TOK][E]
     pdl_trigger();
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const TA* xr = x + (size_t)t * x_stride;
+    const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_wait();
-    const bool vec = rows_vectorise(Wr, xr, K, (size_t)K, (size_t)x_stride) && (wg == nullptr || (uintptr_t)wg % 16 == 0);
+    const bool vec = rows_vectorise(Wr, x, K, (size_t)K, (size_t)x_stride) && (wg == nullptr || (uintptr_t)wg % 16 == 0);
     for (int e = warp; e < E + (wg ? 1 : 0); e += ROUTE_WARPS) {
-        const float z = warp_dot(e < E ? Wr + (size_t)e * K : wg, xr, K, lane, vec);
-        if (lane == 0) {
-            if (e < E) sc[e] = score_kind == 0 ? 1.0f / (1.0f + expf(-z)) : z;
-            else if (ZLM_CHK(gate + t, 4)) gate[t] = 1.0f / (1.0f + expf(-z));
+        const TA* w = e < E ? Wr + (size_t)e * K : wg;
+        float acc[TOK];
+#pragma unroll
+        for (int j = 0; j < TOK; ++j) acc[j] = 0.f;
+        if (vec) {
+            for (int k = lane * 8; k < K; k += 256) {
+                if (!ZLM_CHK(w + k, 8 * sizeof(TA))) continue;
+                float a[8], b[8];
+                load8(w + k, a);
+#pragma unroll
+                for (int j = 0; j < TOK; ++j) {
+                    const TA* xr = x + (size_t)min(t0 + j, T - 1) * x_stride;
+                    if (!ZLM_CHK(xr + k, 8 * sizeof(TA))) continue;
+                    load8(xr + k, b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[j] = fmaf(a[i], b[i], acc[j]);
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                if (!ZLM_CHK(w + k, sizeof(TA))) continue;
+                const float a = to_f32(w[k]);
+#pragma unroll
+                for (int j = 0; j < TOK; ++j) {
+                    const TA* xr = x + (size_t)min(t0 + j, T - 1) * x_stride;
+                    if (ZLM_CHK(xr + k, sizeof(TA))) acc[j] = fmaf(a, to_f32(xr[k]), acc[j]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < TOK; ++j) {
+            const float z = warp_sum(acc[j]);
+            if (lane == 0 && t0 + j < T) {
+                if (e < E) sc_all[j * E + e] = score_kind == 0 ? 1.0f / (1.0f + expf(-z)) : z;
+                else if (ZLM_CHK(gate + t0 + j, 4)) gate[t0 + j] = 1.0f / (1.0f + expf(-z));
+            }
         }
     }
     __syncthreads();
-    if (warp != 0) return;
+    if (warp >= TOK || t0 + warp >= T) return;
+    const int t = t0 + warp;
+    float* sc = sc_all + warp * E;
     if (score_kind == 1) {
         float mx = -INFINITY;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
         mx = warp_max(mx);
         float sum = 0.f;
         for (int e = 0; e < E; ++e) sum += expf(sc[e] - mx);      // one order for all lanes
+        __syncwarp();
         for (int e = lane; e < E; e += 32) sc[e] = expf(sc[e] - mx) / sum;
         __syncwarp();
     }
@@ -107,20 +144,29 @@ moe_route_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restri
         for (int j = 0; j < top; ++j) wgt[(size_t)t * top + j] /= chosen_sum;
 }
 
+template <typename TA>
+static void launch_route(int* idx, float* wgt, float* gate, const void* x, int x_stride, const void* Wr, const void* wg,
+                         int T, int E, int K, int top, int score_kind, int renorm, cudaStream_t st) {
+    // many tokens: four a block (a quarter of the reads of the router's matrix); few: one, so that the blocks are many
+    if (T >= 64)
+        zlm_launch(moe_route_kernel<TA, 4>, (T + 3) / 4, ROUTE_WARPS * 32, (size_t)4 * E * sizeof(float), st, idx, wgt, gate,
+                   (const TA*)x, x_stride, (const TA*)Wr, (const TA*)wg, T, E, K, top, score_kind, renorm);
+    else
+        zlm_launch(moe_route_kernel<TA, 1>, T, ROUTE_WARPS * 32, (size_t)E * sizeof(float), st, idx, wgt, gate, (const TA*)x,
+                   x_stride, (const TA*)Wr, (const TA*)wg, T, E, K, top, score_kind, renorm);
+}
+
 extern "C" int zlm_moe_route(int* idx, float* wgt, float* gate, const void* x, int x_stride, const void* Wr,
                              const void* wg, int dtype, int T, int E, int K, int top, int score_kind, int renorm,
                              cudaStream_t st) {
     if (T == 0) return ZLM_OK;
-    ZLM_REQUIRE(E > 0 && E <= 8192 && K > 0 && top > 0 && top <= E, "moe_route: experts=%d top=%d K=%d", E, top, K);
+    ZLM_REQUIRE(E > 0 && E <= 2048 && K > 0 && top > 0 && top <= E, "moe_route: experts=%d top=%d K=%d", E, top, K);
     ZLM_REQUIRE(score_kind == 0 || score_kind == 1, "moe_route: score kind %d", score_kind);
     ZLM_REQUIRE(wg == nullptr || gate != nullptr, "moe_route: a shared gate needs a place for its values");
-    const size_t smem = (size_t)E * sizeof(float);
     if (dtype == ZLM_DTYPE_F32)
-        zlm_launch(moe_route_kernel<float>, T, ROUTE_WARPS * 32, smem, st, idx, wgt, gate, (const float*)x, x_stride,
-                   (const float*)Wr, (const float*)wg, E, K, top, score_kind, renorm);
+        launch_route<float>(idx, wgt, gate, x, x_stride, Wr, wg, T, E, K, top, score_kind, renorm, st);
     else if (dtype == ZLM_DTYPE_BF16)
-        zlm_launch(moe_route_kernel<__nv_bfloat16>, T, ROUTE_WARPS * 32, smem, st, idx, wgt, gate, (const __nv_bfloat16*)x,
-                   x_stride, (const __nv_bfloat16*)Wr, (const __nv_bfloat16*)wg, E, K, top, score_kind, renorm);
+        launch_route<__nv_bfloat16>(idx, wgt, gate, x, x_stride, Wr, wg, T, E, K, top, score_kind, renorm, st);
     else
         ZLM_REQUIRE(false, "moe_route: unsupported dtype %d", dtype);
     return zlm_check_launch("moe_route");

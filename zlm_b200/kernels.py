@@ -96,6 +96,22 @@ def decode_splits(rows: int, nkv: int, len_bucket: int, blocks: int = 148 * DECO
     return splits, per
 
 
+def latent_decode_splits(rows: int, tiles: int, len_bucket: int, wave: int):
+    """How the latent attention's decode step cuts a sequence's pages: (splits, pages per split).  A page of
+    records is several times a page of one kv head's keys, a block holds two of them in flight and an SM holds
+    few such blocks (``wave``: what the device holds at a time), so a block's own chain of pages is what a
+    step waits for: as many splits as fill one wave, of two pages at least (one more kernel, the combine, reads
+    every split's partial result)."""
+    pairs = max(1, rows * tiles)
+    per = max(2, -(-len_bucket * pairs // max(1, wave)))
+    per = min(per, max(1, len_bucket))
+    splits = -(-len_bucket // per)
+    while splits > 1024:
+        per *= 2
+        splits = -(-len_bucket // per)
+    return splits, per
+
+
 def _dt(t: torch.Tensor) -> int:
     try:
         return _DT[t.dtype]
@@ -727,7 +743,9 @@ class CudaKernels:
             if plan.is_decode:
                 if len_bucket is None:
                     len_bucket = attention_len_bucket(plan.max_len)
-                splits, per = decode_splits(T, tiles, len_bucket, self.decode_blocks or self.sm_count * DECODE_BLOCKS_PER_SM)
+                wave = self.decode_blocks or self.sm_count * int(
+                    self.lib.zlm_latent_attention_mma_blocks_per_sm(c_int(kv_rank), c_int(rot_dim)))
+                splits, per = latent_decode_splits(T, tiles, len_bucket, wave)
                 qt, fresh = 1, max(1, int(getattr(plan, "max_new", 1) or 1))
             else:
                 splits, per = 1, max(1, (int(plan.max_len) + PAGE_TOKENS - 1) // PAGE_TOKENS)

@@ -30,6 +30,8 @@ from .base import CacheRequest, LayerIO, Mixer, ParamSpec, StepContext
 
 @register_mixer("latent_attention")
 class LatentAttention(Mixer):
+    reads_input_by_products = True       # x goes into the fused q / latent projection and nowhere else
+
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_dim: int, kv_rank: int,
                  scale: float, norm_eps: float = 1e-6, window: int = 0,
                  position: Optional[Mapping[str, Any]] = None, kv_proj: bool = True):
