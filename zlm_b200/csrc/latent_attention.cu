@@ -112,9 +112,21 @@ extern "C" int zlm_latent_prep(const void* q, int q_stride, void* qo, int qo_str
 
 // ---------------------------------------------------------------------------- per-head products
 // out[t, h, n] = sum_k x[t, h, k] * W[h, n, k]; a warp owns one (h, n) and eight tokens at a time, its lanes
-// share k, so a sum's order depends on K alone.
+// share k, so a sum's order depends on K (and the operands' alignment) alone, never on the batch.
 #define HL_TOK 8
-template <typename TA>
+__device__ __forceinline__ void hl_load4(const float* p, float* f) {
+    const float4 v = *(const float4*)p;
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+__device__ __forceinline__ void hl_load4(const __nv_bfloat16* p, float* f) {
+    const uint2 v = *(const uint2*)p;
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+
+// VEC: K and the strides are multiples of 4 and the operands aligned for loads of four elements: a lane takes
+// four neighbouring k at a time (one load of W for eight tokens' loads of x); else one k at a time.
+template <typename TA, bool VEC>
 __global__ void __launch_bounds__(128)
 head_linear_kernel(TA* __restrict__ out, int out_stride, int out_hstride, const TA* __restrict__ x, int x_stride,
                    int x_hstride, const TA* __restrict__ W, int T, int H, int N, int K) {
@@ -128,14 +140,32 @@ head_linear_kernel(TA* __restrict__ out, int out_stride, int out_hstride, const 
         float acc[HL_TOK];
 #pragma unroll
         for (int j = 0; j < HL_TOK; ++j) acc[j] = 0.f;
-        for (int k = lane; k < K; k += 32) {
-            if (!ZLM_CHK(w + k, sizeof(TA))) continue;
-            const float wv = to_f32(w[k]);
+        if (VEC) {
+            for (int k = lane * 4; k < K; k += 128) {
+                if (!ZLM_CHK(w + k, 4 * sizeof(TA))) continue;
+                float wv[4], xv[4];
+                hl_load4(w + k, wv);
 #pragma unroll
-            for (int j = 0; j < HL_TOK; ++j) {
-                const int t = t0 + j;
-                if (t < T && ZLM_CHK(x + (size_t)t * x_stride + (size_t)h * x_hstride + k, sizeof(TA)))
-                    acc[j] = fmaf(to_f32(x[(size_t)t * x_stride + (size_t)h * x_hstride + k]), wv, acc[j]);
+                for (int j = 0; j < HL_TOK; ++j) {
+                    const int t = t0 + j;
+                    const TA* xp = x + (size_t)t * x_stride + (size_t)h * x_hstride + k;
+                    if (t < T && ZLM_CHK(xp, 4 * sizeof(TA))) {
+                        hl_load4(xp, xv);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[j] = fmaf(xv[i], wv[i], acc[j]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32) {
+                if (!ZLM_CHK(w + k, sizeof(TA))) continue;
+                const float wv = to_f32(w[k]);
+#pragma unroll
+                for (int j = 0; j < HL_TOK; ++j) {
+                    const int t = t0 + j;
+                    if (t < T && ZLM_CHK(x + (size_t)t * x_stride + (size_t)h * x_hstride + k, sizeof(TA)))
+                        acc[j] = fmaf(to_f32(x[(size_t)t * x_stride + (size_t)h * x_hstride + k]), wv, acc[j]);
+                }
             }
         }
 #pragma unroll
@@ -148,6 +178,19 @@ head_linear_kernel(TA* __restrict__ out, int out_stride, int out_hstride, const 
     }
 }
 
+template <typename TA>
+static void launch_head_linear(dim3 grid, cudaStream_t st, void* out, int out_stride, int out_hstride, const void* x,
+                               int x_stride, int x_hstride, const void* W, int T, int H, int N, int K) {
+    const size_t quad = 4 * sizeof(TA);
+    const bool vec = K % 4 == 0 && x_stride % 4 == 0 && x_hstride % 4 == 0 && (uintptr_t)x % quad == 0 && (uintptr_t)W % quad == 0;
+    if (vec)
+        zlm_launch(head_linear_kernel<TA, true>, grid, 128, 0, st, (TA*)out, out_stride, out_hstride, (const TA*)x, x_stride,
+                   x_hstride, (const TA*)W, T, H, N, K);
+    else
+        zlm_launch(head_linear_kernel<TA, false>, grid, 128, 0, st, (TA*)out, out_stride, out_hstride, (const TA*)x, x_stride,
+                   x_hstride, (const TA*)W, T, H, N, K);
+}
+
 extern "C" int zlm_head_linear(void* out, int out_stride, int out_hstride, const void* x, int x_stride, int x_hstride,
                                const void* W, int dtype, int T, int H, int N, int K, cudaStream_t st) {
     if (T == 0 || N == 0) return ZLM_OK;
@@ -156,11 +199,9 @@ extern "C" int zlm_head_linear(void* out, int out_stride, int out_hstride, const
     if (tz > 64) tz = 64;
     dim3 grid((N + 3) / 4, H, tz);
     if (dtype == ZLM_DTYPE_F32)
-        zlm_launch(head_linear_kernel<float>, grid, 128, 0, st, (float*)out, out_stride, out_hstride, (const float*)x,
-                   x_stride, x_hstride, (const float*)W, T, H, N, K);
+        launch_head_linear<float>(grid, st, out, out_stride, out_hstride, x, x_stride, x_hstride, W, T, H, N, K);
     else if (dtype == ZLM_DTYPE_BF16)
-        zlm_launch(head_linear_kernel<__nv_bfloat16>, grid, 128, 0, st, (__nv_bfloat16*)out, out_stride, out_hstride,
-                   (const __nv_bfloat16*)x, x_stride, x_hstride, (const __nv_bfloat16*)W, T, H, N, K);
+        launch_head_linear<__nv_bfloat16>(grid, st, out, out_stride, out_hstride, x, x_stride, x_hstride, W, T, H, N, K);
     else
         ZLM_REQUIRE(false, "head_linear: unsupported dtype %d", dtype);
     return zlm_check_launch("head_linear");
