@@ -164,3 +164,23 @@ def test_trace_replay_runs_the_design(tmp_path):
     V = cfg["vocab"]
     assert_rows_close(torch.from_numpy(got0.reshape(-1, V).copy()), torch.stack([wa[0], wa[18], wb[7]]), "float32")
     assert_rows_close(torch.from_numpy(got1.reshape(-1, V).copy()), wa[19:20], "float32")
+
+
+def test_command_line_writes_and_runs_a_random_model(tmp_path, capsys):
+    """``random-model`` from a Nuvilorn config.json, then ``run`` on the folder it wrote: the tokens are those of
+    ``Engine.generate`` on the same folder."""
+    import json
+    from zlm_b200 import Engine
+    from zlm_b200.cli import main
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(NUVI["A"]))
+    folder = str(tmp_path / "model")
+    assert main(["random-model", "--config", str(cfg_path), "--seed", "3", "--out", folder]) == 0
+    capsys.readouterr()
+    assert main(["run", folder, "-p", "5 17 3", "-p", "9 9", "--max-tokens", "6", "--dtype", "float32"]) == 0
+    lines = [l.split("\t") for l in capsys.readouterr().out.splitlines() if "\t" in l and l[0].isdigit()]
+    got = {0: [], 1: []}
+    for req, tok in lines:
+        got[int(req)].append(int(tok))
+    want = Engine.from_pretrained(folder, dtype="float32", max_tokens=256).generate([[5, 17, 3], [9, 9]], max_tokens=6).tokens
+    assert [got[0], got[1]] == want

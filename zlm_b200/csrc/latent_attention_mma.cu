@@ -4,10 +4,10 @@
 // of records, staged once in shared memory, serves as keys (all D columns) and as values (the
 // first r columns).
 //
-// grid (token group, head tile, split).  A block has QT groups of 4 warps; group i works on token
+// grid (token group, head tile, split).  A block has QT groups of 4 or 8 warps; group i works on token
 // t0 + i, and all groups share the staged pages (tokens of one block that belong to different
 // sequences are walked one sequence after the other).  Per page of 64 records a group computes
-//   S = Q K^T     each warp 16 keys, Q fragments from shared memory (D is too wide for registers)
+//   S = Q K^T     each warp 16 keys (8 in groups of 8 warps), Q fragments from shared memory (D is too wide for registers)
 //   the page's row maxima across the four warps, P = exp2(S - m) as bf16 in shared memory
 //   O += P V      each warp all 64 keys for its share of the r value columns (units of 16 columns
 //                 dealt round-robin), so no warp holds more than 16 x 16 NU accumulators
@@ -17,31 +17,36 @@
 #include "common.cuh"
 #include "attn_common.cuh"
 
-#define LM_GROUP 128           // threads of a group (4 warps)
 #define LM_PAD 8               // elements of padding per shared-memory row: rows 16 bytes apart in the banks
 
-template <int NU, int QT>
-__global__ void __launch_bounds__(LM_GROUP * QT)
+// GW: warps of a group (4: each takes 16 of a page's keys, two score tiles; 8: 8 keys, one score tile, and half
+// as many value columns a warp, for sizes whose shared memory leaves room for few tokens a block: twice the
+// warps an SM holds)
+template <int NU, int QT, int GW>
+__global__ void __launch_bounds__(GW * 32 * QT)
 latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bfloat16* __restrict__ q, int q_stride,
                   const __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table, int table_stride,
                   const int* __restrict__ token_pos, const int* __restrict__ token_slot, int T, int H, int r, int dr,
                   float scale_log2, int window, int splits, int per, float* __restrict__ part_o,
                   float* __restrict__ part_ml, int fresh) {
+    constexpr int GT = GW * 32;                  // threads of a group
+    constexpr int NTK = 8 / GW;                  // score tiles (of 8 keys) a warp takes of a page
+    constexpr int WK = 8 * NTK;                  // keys a warp takes of a page
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int D = r + dr, DS = D + LM_PAD, PS = ZLM_PAGE + LM_PAD;
     const int KS = D / 16, NV = r / 16;
     __nv_bfloat16* Rs = (__nv_bfloat16*)smem_raw;                         // [2][64][DS] the staged pages
     __nv_bfloat16* Qs = Rs + 2 * ZLM_PAGE * DS;                           // [QT][16][DS]
     __nv_bfloat16* Ps = Qs + QT * 16 * DS;                                // [QT][16][PS]
-    float* smax = (float*)(Ps + QT * 16 * PS);                            // [QT][4][16], later the warps' sums
+    float* smax = (float*)(Ps + QT * 16 * PS);                            // [QT][GW][16], later the warps' sums
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int grp = warp >> 2, wq = warp & 3, gtid = tid & (LM_GROUP - 1);
+    const int grp = warp / GW, wq = warp % GW;
     const int g = lane >> 2, qd = lane & 3;
     // prompts: the last tokens of a sequence walk the most pages, so their blocks go first (blocks start in
     // the order of their index) and the short ones fill in behind them
     const int t0 = (QT > 1 ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x) * QT, htile = blockIdx.y, split = blockIdx.z;
-    const GroupSync gsync{1 + grp, LM_GROUP};
+    const GroupSync gsync{1 + grp, GT};
     pdl_launch_dependents();
 
     const int my_t = t0 + grp;
@@ -58,7 +63,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
         const __nv_bfloat16* src = pool + (size_t)pages[p] * ZLM_PAGE * D;
         __nv_bfloat16* dst = Rs + (size_t)stage * ZLM_PAGE * DS;
         const int CH = D / 8;
-        for (int id = tid; id < ZLM_PAGE * CH; id += LM_GROUP * QT) {
+        for (int id = tid; id < ZLM_PAGE * CH; id += GT * QT) {
             const int row = id / CH, c = id - row * CH;
             dec_cp_async16(dst + row * DS + c * 8, src + (size_t)row * D + c * 8);
         }
@@ -118,7 +123,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
         if (!q_loaded) {
             // the 16 heads of this tile for every group's token (zero rows beyond the last head or token)
             const int CH = D / 8;
-            for (int id = tid; id < QT * 16 * CH; id += LM_GROUP * QT) {
+            for (int id = tid; id < QT * 16 * CH; id += GT * QT) {
                 const int gi = id / (16 * CH), rem = id - gi * 16 * CH, row = rem / CH, c = rem - row * CH;
                 const int head = htile * 16 + row, t = t0 + gi;
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -138,50 +143,66 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
                 const __nv_bfloat16* rt = Rs + (size_t)stage * ZLM_PAGE * DS;
                 const __nv_bfloat16* qt = Qs + (size_t)grp * 16 * DS;
                 __nv_bfloat16* pt = Ps + (size_t)grp * 16 * PS;
-                float* mx = smax + grp * 64;
-                float s[2][4];
+                float* mx = smax + grp * GW * 16;
+                // two chains of sums, even and odd steps of 16 columns (a product waits for the one before it in
+                // its chain), added at the end
+                float s[NTK][4], s2[NTK][4];
 #pragma unroll
-                for (int i = 0; i < 2; ++i)
+                for (int i = 0; i < NTK; ++i)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) s[i][e] = 0.f;
+                    for (int e = 0; e < 4; ++e) s[i][e] = s2[i][e] = 0.f;
                 const int mi = lane >> 3;
                 const int a_row = (lane & 7) + (mi & 1) * 8, a_chunk = mi >> 1;
-                const int b_row = wq * 16 + (mi >> 1) * 8 + (lane & 7), b_chunk = mi & 1;
-                // (two chains of sums, even and odd steps of 16 columns: a product waits for the one before it
-                // in its chain, and D / 16 steps in one chain are most of a page's time)
-                float s2[2][4];
-#pragma unroll
-                for (int i = 0; i < 2; ++i)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) s2[i][e] = 0.f;
+                if (GW == 4) {
+                    const int b_row = wq * 16 + (mi >> 1) * 8 + (lane & 7), b_chunk = mi & 1;
 #pragma unroll 2
-                for (int ks = 0; ks + 1 < KS; ks += 2) {
-                    unsigned a[4], c[4], b00, b01, b10, b11, d00, d01, d10, d11;
-                    dec_ldsm4(a[0], a[1], a[2], a[3], qt + a_row * DS + (ks * 2 + a_chunk) * 8);
-                    dec_ldsm4(b00, b01, b10, b11, rt + b_row * DS + (ks * 2 + b_chunk) * 8);
-                    dec_ldsm4(c[0], c[1], c[2], c[3], qt + a_row * DS + (ks * 2 + 2 + a_chunk) * 8);
-                    dec_ldsm4(d00, d01, d10, d11, rt + b_row * DS + (ks * 2 + 2 + b_chunk) * 8);
-                    dec_mma(s[0], a, b00, b01);
-                    dec_mma(s[1], a, b10, b11);
-                    dec_mma(s2[0], c, d00, d01);
-                    dec_mma(s2[1], c, d10, d11);
-                }
-                if (KS & 1) {
-                    const int ks = KS - 1;
-                    unsigned a[4], b00, b01, b10, b11;
-                    dec_ldsm4(a[0], a[1], a[2], a[3], qt + a_row * DS + (ks * 2 + a_chunk) * 8);
-                    dec_ldsm4(b00, b01, b10, b11, rt + b_row * DS + (ks * 2 + b_chunk) * 8);
-                    dec_mma(s[0], a, b00, b01);
-                    dec_mma(s[1], a, b10, b11);
+                    for (int ks = 0; ks + 1 < KS; ks += 2) {
+                        unsigned a[4], c[4], b00, b01, b10, b11, d00, d01, d10, d11;
+                        dec_ldsm4(a[0], a[1], a[2], a[3], qt + a_row * DS + (ks * 2 + a_chunk) * 8);
+                        dec_ldsm4(b00, b01, b10, b11, rt + b_row * DS + (ks * 2 + b_chunk) * 8);
+                        dec_ldsm4(c[0], c[1], c[2], c[3], qt + a_row * DS + (ks * 2 + 2 + a_chunk) * 8);
+                        dec_ldsm4(d00, d01, d10, d11, rt + b_row * DS + (ks * 2 + 2 + b_chunk) * 8);
+                        dec_mma(s[0], a, b00, b01);
+                        dec_mma(s[NTK - 1], a, b10, b11);
+                        dec_mma(s2[0], c, d00, d01);
+                        dec_mma(s2[NTK - 1], c, d10, d11);
+                    }
+                    if (KS & 1) {
+                        const int ks = KS - 1;
+                        unsigned a[4], b00, b01, b10, b11;
+                        dec_ldsm4(a[0], a[1], a[2], a[3], qt + a_row * DS + (ks * 2 + a_chunk) * 8);
+                        dec_ldsm4(b00, b01, b10, b11, rt + b_row * DS + (ks * 2 + b_chunk) * 8);
+                        dec_mma(s[0], a, b00, b01);
+                        dec_mma(s[NTK - 1], a, b10, b11);
+                    }
+                } else {
+                    // 8 keys a warp: one load brings the key fragments of two steps (columns ks*16 .. ks*16+31)
+                    const int b_row = wq * 8 + (lane & 7);
+#pragma unroll 2
+                    for (int ks = 0; ks + 1 < KS; ks += 2) {
+                        unsigned a[4], c[4], b0, b1, b2, b3;
+                        dec_ldsm4(a[0], a[1], a[2], a[3], qt + a_row * DS + (ks * 2 + a_chunk) * 8);
+                        dec_ldsm4(c[0], c[1], c[2], c[3], qt + a_row * DS + (ks * 2 + 2 + a_chunk) * 8);
+                        dec_ldsm4(b0, b1, b2, b3, rt + b_row * DS + (ks * 2 + mi) * 8);
+                        dec_mma(s[0], a, b0, b1);
+                        dec_mma(s2[0], c, b2, b3);
+                    }
+                    if (KS & 1) {
+                        const int ks = KS - 1;
+                        unsigned a[4], b0, b1, b2, b3;
+                        dec_ldsm4(a[0], a[1], a[2], a[3], qt + a_row * DS + (ks * 2 + a_chunk) * 8);
+                        dec_ldsm4(b0, b1, b2, b3, rt + b_row * DS + (ks * 2 + (mi & 1)) * 8);      // (the last two repeat the first)
+                        dec_mma(s[0], a, b0, b1);
+                    }
                 }
 #pragma unroll
-                for (int i = 0; i < 2; ++i)
+                for (int i = 0; i < NTK; ++i)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) s[i][e] += s2[i][e];
-                const int kbase = p * ZLM_PAGE + wq * 16;
+                const int kbase = p * ZLM_PAGE + wq * WK;
                 float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
+                for (int nt = 0; nt < NTK; ++nt)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int key = kbase + nt * 8 + qd * 2 + e;
@@ -200,8 +221,12 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
                     mx[wq * 16 + g + 8] = mx1;
                 }
                 gsync.sync();
-                float pm0 = fmaxf(fmaxf(mx[g], mx[16 + g]), fmaxf(mx[32 + g], mx[48 + g]));
-                float pm1 = fmaxf(fmaxf(mx[g + 8], mx[16 + g + 8]), fmaxf(mx[32 + g + 8], mx[48 + g + 8]));
+                float pm0 = -INFINITY, pm1 = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < GW; ++w) {
+                    pm0 = fmaxf(pm0, mx[w * 16 + g]);
+                    pm1 = fmaxf(pm1, mx[w * 16 + g + 8]);
+                }
                 const float mn0 = fmaxf(m0, pm0), mn1 = fmaxf(m1, pm1);        // finite: the page has a key in reach
                 const float a0 = m0 == -INFINITY ? 0.f : exp2f(m0 - mn0);
                 const float a1 = m1 == -INFINITY ? 0.f : exp2f(m1 - mn1);
@@ -209,7 +234,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
                 m1 = mn1;
                 float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
+                for (int nt = 0; nt < NTK; ++nt) {
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         s[nt][e] = s[nt][e] == -INFINITY ? 0.f : exp2f(s[nt][e] - mn0);
@@ -217,7 +242,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
                         ps0 += s[nt][e];
                         ps1 += s[nt][2 + e];
                     }
-                    const int col = wq * 16 + nt * 8 + qd * 2;
+                    const int col = wq * WK + nt * 8 + qd * 2;
                     *(unsigned*)(pt + g * PS + col) = pack_bf16(s[nt][0], s[nt][1]);
                     *(unsigned*)(pt + (g + 8) * PS + col) = pack_bf16(s[nt][2], s[nt][3]);
                 }
@@ -227,7 +252,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
                 for (int i = 0; i < 2 * NU; ++i) {
                     o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1;
                 }
-                gsync.sync();                        // P of all four warps is there
+                gsync.sync();                        // P of all the group's warps is there
                 const int v_row = (mi & 1) * 8 + (lane & 7), v_chunk = mi >> 1;
 #pragma unroll
                 for (int kk = 0; kk < ZLM_PAGE / 16; ++kk) {
@@ -235,7 +260,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
                     dec_ldsm4(a[0], a[1], a[2], a[3], pt + a_row * PS + (kk * 2 + a_chunk) * 8);
 #pragma unroll
                     for (int j = 0; j < NU; ++j) {
-                        const int u = wq + 4 * j;
+                        const int u = wq + GW * j;
                         if (u < NV) {
                             unsigned b0, b1, b2, b3;
                             dec_ldsm4t(b0, b1, b2, b3, rt + (kk * 16 + v_row) * DS + (u * 2 + v_chunk) * 8);
@@ -255,23 +280,27 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
     __syncthreads();
     if (!have || my_slot < 0) return;
 
-    // the four warps' sums of a row in a fixed order
+    // the group's warps' sums of a row in a fixed order
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    float* sl = smax + grp * 64;
+    float* sl = smax + grp * GW * 16;
     if (qd == 0) {
         sl[wq * 16 + g] = l0;
         sl[wq * 16 + g + 8] = l1;
     }
     gsync.sync();
-    const float L0 = ((sl[g] + sl[16 + g]) + sl[32 + g]) + sl[48 + g];
-    const float L1 = ((sl[g + 8] + sl[16 + g + 8]) + sl[32 + g + 8]) + sl[48 + g + 8];
+    float L0 = 0.f, L1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < GW; ++w) {
+        L0 += sl[w * 16 + g];
+        L1 += sl[w * 16 + g + 8];
+    }
     const int h0 = htile * 16 + g, h1 = h0 + 8;
 #pragma unroll
     for (int j = 0; j < NU; ++j) {
-        const int u = wq + 4 * j;
+        const int u = wq + GW * j;
         if (u >= NV) continue;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -313,7 +342,7 @@ extern "C" int zlm_attention_decode_combine(void* out, int out_stride, const flo
 
 static size_t latent_mma_smem(int D, int QT) {
     const size_t DS = D + LM_PAD, PS = ZLM_PAGE + LM_PAD;
-    return (2 * ZLM_PAGE * DS + (size_t)QT * 16 * DS + (size_t)QT * 16 * PS) * 2 + (size_t)QT * 64 * 4;
+    return (2 * ZLM_PAGE * DS + (size_t)QT * 16 * DS + (size_t)QT * 16 * PS) * 2 + (size_t)QT * 8 * 16 * 4;
 }
 
 // 1 if the tensor-core kernel takes the shape (else the caller uses the plain kernel)
@@ -336,13 +365,13 @@ extern "C" int zlm_latent_attention_mma_tokens(int r, int dr) {
     return 1;
 }
 
-template <int NU, int QT>
+template <int NU, int QT, int GW>
 static int launch_latent_mma(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                              const int* block_table, int table_stride, const int* token_pos, const int* token_slot,
                              int T, int H, int r, int dr, float scale, int window, int splits, int per, float* part_o,
                              float* part_ml, int fresh, cudaStream_t st) {
     const size_t smem = latent_mma_smem(r + dr, QT);
-    auto kern = latent_mma_kernel<NU, QT>;
+    auto kern = latent_mma_kernel<NU, QT, GW>;
     static size_t reserved[64] = {};
     size_t& have = reserved[zlm_device_index()];
     if (smem > have) {
@@ -354,7 +383,7 @@ static int launch_latent_mma(void* out, int out_stride, const void* q, int q_str
         have = smem;
     }
     dim3 grid((T + QT - 1) / QT, (H + 15) / 16, splits);
-    zlm_launch(kern, grid, dim3(LM_GROUP * QT), smem, st, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
+    zlm_launch(kern, grid, dim3(GW * 32 * QT), smem, st, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                (const __nv_bfloat16*)pool, block_table, table_stride, token_pos, token_slot, T, H, r, dr,
                scale * 1.4426950408889634f, window, splits, per, part_o, part_ml, fresh);
     int rc = zlm_check_launch("latent_attention_mma");
@@ -380,21 +409,27 @@ extern "C" int zlm_latent_attention_mma(void* out, int out_stride, const void* q
     ZLM_REQUIRE((uintptr_t)q % 16 == 0 && (q_stride * 2) % 16 == 0 && ((r + dr) * 2) % 16 == 0 && (uintptr_t)out % 4 == 0 &&
                 out_stride % 2 == 0, "latent_attention_mma: q must be 16-byte aligned, out 4-byte aligned");
     ZLM_REQUIRE((H + 15) / 16 <= 65535 && splits <= 65535, "latent_attention_mma: too many head tiles or splits");
-    const int nu = ((r / 16) + 3) / 4;
-#define ZLM_LM(NU, QT)                                                                                               \
-    return launch_latent_mma<NU, QT>(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,      \
-                                     token_slot, T, H, r, dr, scale, window, splits, per, part_o, part_ml, fresh, st)
-#define ZLM_LM_Q(QT)                              \
+    // groups of 8 warps where a block has one or two tokens (large records: twice the warps an SM holds, half the
+    // value columns a warp); groups of 4 where four tokens fit
+    const int nu4 = ((r / 16) + 3) / 4, nu8 = ((r / 16) + 7) / 8;
+#define ZLM_LM(NU, QT, GW)                                                                                           \
+    return launch_latent_mma<NU, QT, GW>(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,  \
+                                         token_slot, T, H, r, dr, scale, window, splits, per, part_o, part_ml, fresh, st)
+#define ZLM_LM_8(QT)                              \
     do {                                          \
-        if (nu <= 1) ZLM_LM(1, QT);               \
-        if (nu <= 2) ZLM_LM(2, QT);               \
-        if (nu <= 4) ZLM_LM(4, QT);               \
-        ZLM_LM(8, QT);                            \
+        if (nu8 <= 1) ZLM_LM(1, QT, 8);           \
+        if (nu8 <= 2) ZLM_LM(2, QT, 8);           \
+        ZLM_LM(4, QT, 8);                         \
     } while (0)
-    if (tokens_per_block == 1) ZLM_LM_Q(1);
-    if (tokens_per_block == 2) ZLM_LM_Q(2);
-    if (tokens_per_block == 4) ZLM_LM_Q(4);
-#undef ZLM_LM_Q
+    if (tokens_per_block == 1) ZLM_LM_8(1);
+    if (tokens_per_block == 2) ZLM_LM_8(2);
+    if (tokens_per_block == 4) {
+        if (nu4 <= 1) ZLM_LM(1, 4, 4);
+        if (nu4 <= 2) ZLM_LM(2, 4, 4);
+        if (nu4 <= 4) ZLM_LM(4, 4, 4);
+        ZLM_LM(8, 4, 4);
+    }
+#undef ZLM_LM_8
 #undef ZLM_LM
     ZLM_REQUIRE(false, "latent_attention_mma: %d tokens a block (1, 2 or 4)", tokens_per_block);
 }
