@@ -235,7 +235,7 @@ static int launch_prefill(__nv_bfloat16* out, int out_stride, const __nv_bfloat1
 }
 
 extern "C" int zlm_attention_prefill_supported(int nq, int nkv, int hd) {
-    return (nkv > 0 && nq % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 128) ? 1 : 0;
+    return (nkv > 0 && nq % nkv == 0 && hd % 16 == 0 && hd >= 16 && hd <= 192) ? 1 : 0;
 }
 
 // q tokens are packed by sequence: sequence r owns tokens cu_seqlens[r] .. cu_seqlens[r+1]-1 at positions
@@ -256,7 +256,7 @@ extern "C" int zlm_attention_prefill(void* out, int out_stride, const void* q, i
                                  seq_start, R, max_new, nq, nkv, scale, window, st);
     switch (hd) {
         ZLM_PRE_CASE(16) ZLM_PRE_CASE(32) ZLM_PRE_CASE(48) ZLM_PRE_CASE(64) ZLM_PRE_CASE(80) ZLM_PRE_CASE(96)
-        ZLM_PRE_CASE(112) ZLM_PRE_CASE(128)
+        ZLM_PRE_CASE(112) ZLM_PRE_CASE(128) ZLM_PRE_CASE(144) ZLM_PRE_CASE(160) ZLM_PRE_CASE(176) ZLM_PRE_CASE(192)
     }
 #undef ZLM_PRE_CASE
     ZLM_REQUIRE(false, "attention_prefill: head_dim=%d", hd);

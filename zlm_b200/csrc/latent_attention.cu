@@ -342,4 +342,91 @@ extern "C" int zlm_latent_attention(void* out, int out_stride, const void* q, in
     return ZLM_OK;
 }
 
+// ---------------------------------------------------------------------------- unfolded keys and values of a step
+// For whole prompts the per-head keys and values of the step's own tokens may be written out once, so that the
+// library's flash attention over per-head keys and values serves the step (fewer flops than the folded form by
+// (kv_rank + rot_dim + kv_rank) / (dim + rot_dim + v_dim)):
+//   latent_gather    rec[t, :] = the record of token t from the paged pool
+//   latent_unfold    K[page, h, place, :] = [kn[t, h, :dn] | kr[t, :dr]],  V[page, h, place, :] = [v[t, h, :dv] | 0]
+//                    into a pool of the attention kernels' layout [pages, 2, H, 64, hd], hd = dn + dr, pages by a
+//                    table of the step's own (row = the sequence's number in the step)
+template <typename TA>
+__global__ void __launch_bounds__(128)
+latent_gather_kernel(TA* __restrict__ rec, const TA* __restrict__ pool, const int* __restrict__ block_table,
+                     int table_stride, const int* __restrict__ token_pos, const int* __restrict__ token_slot, int R) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_slot + t, 4)) return;
+    const int pos = token_pos[t], slot = token_slot[t];
+    if (!ZLM_CHK(block_table + (size_t)slot * table_stride + pos / ZLM_PAGE, 4)) return;
+    const int page = block_table[(size_t)slot * table_stride + pos / ZLM_PAGE];
+    pdl_wait();
+    const TA* src = pool + ((size_t)page * ZLM_PAGE + pos % ZLM_PAGE) * R;
+    TA* dst = rec + (size_t)t * R;
+    for (int i = threadIdx.x; i < R; i += blockDim.x)
+        if (ZLM_CHK(src + i, sizeof(TA)) && ZLM_CHK(dst + i, sizeof(TA))) dst[i] = src[i];
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+latent_unfold_kernel(TA* __restrict__ spool, const int* __restrict__ stable, int stable_stride, const TA* __restrict__ kv,
+                     int kv_stride, const TA* __restrict__ rec, int rec_stride, const int* __restrict__ token_pos,
+                     const int* __restrict__ token_seq, int H, int dn, int dr, int dv, int r) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x, hd = dn + dr;
+    if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_seq + t, 4)) return;
+    const int pos = token_pos[t], seq = token_seq[t];
+    if (!ZLM_CHK(stable + (size_t)seq * stable_stride + pos / ZLM_PAGE, 4)) return;
+    const int page = stable[(size_t)seq * stable_stride + pos / ZLM_PAGE];
+    pdl_wait();
+    const size_t tile = (size_t)ZLM_PAGE * hd;
+    TA* kbase = spool + (size_t)page * 2 * H * tile + (size_t)(pos % ZLM_PAGE) * hd;
+    TA* vbase = kbase + (size_t)H * tile;
+    const TA* kvr = kv + (size_t)t * kv_stride;
+    const TA* kr = rec + (size_t)t * rec_stride + r;
+    for (int e = threadIdx.x; e < H * hd; e += blockDim.x) {
+        const int h = e / hd, i = e - h * hd;
+        TA* kd = kbase + (size_t)h * tile + i;
+        TA* vd = vbase + (size_t)h * tile + i;
+        if (!ZLM_CHK(kd, sizeof(TA)) || !ZLM_CHK(vd, sizeof(TA))) continue;
+        const TA* ks = i < dn ? kvr + (size_t)h * dn + i : kr + (i - dn);
+        *kd = ZLM_CHK(ks, sizeof(TA)) ? *ks : from_f32<TA>(0.f);
+        const TA* vs = kvr + (size_t)H * dn + (size_t)h * dv + i;
+        *vd = (i < dv && ZLM_CHK(vs, sizeof(TA))) ? *vs : from_f32<TA>(0.f);
+    }
+}
+
+extern "C" int zlm_latent_gather(void* rec, const void* pool, const int* block_table, int table_stride,
+                                 const int* token_pos, const int* token_slot, int dtype, int T, int R, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(R > 0, "latent_gather: record of %d elements", R);
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(latent_gather_kernel<float>, T, 128, 0, st, (float*)rec, (const float*)pool, block_table, table_stride,
+                   token_pos, token_slot, R);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(latent_gather_kernel<__nv_bfloat16>, T, 128, 0, st, (__nv_bfloat16*)rec, (const __nv_bfloat16*)pool,
+                   block_table, table_stride, token_pos, token_slot, R);
+    else
+        ZLM_REQUIRE(false, "latent_gather: unsupported dtype %d", dtype);
+    return zlm_check_launch("latent_gather");
+}
+
+extern "C" int zlm_latent_unfold(void* spool, const int* stable, int stable_stride, const void* kv, int kv_stride,
+                                 const void* rec, int rec_stride, const int* token_pos, const int* token_seq, int dtype,
+                                 int T, int H, int dn, int dr, int dv, int r, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(H > 0 && dn >= 0 && dr >= 0 && dn + dr > 0 && dv > 0 && dv <= dn + dr && r > 0,
+                "latent_unfold: heads=%d dim=%d rot_dim=%d v_dim=%d", H, dn, dr, dv);
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(latent_unfold_kernel<float>, T, 256, 0, st, (float*)spool, stable, stable_stride, (const float*)kv, kv_stride,
+                   (const float*)rec, rec_stride, token_pos, token_seq, H, dn, dr, dv, r);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(latent_unfold_kernel<__nv_bfloat16>, T, 256, 0, st, (__nv_bfloat16*)spool, stable, stable_stride,
+                   (const __nv_bfloat16*)kv, kv_stride, (const __nv_bfloat16*)rec, rec_stride, token_pos, token_seq, H, dn, dr,
+                   dv, r);
+    else
+        ZLM_REQUIRE(false, "latent_unfold: unsupported dtype %d", dtype);
+    return zlm_check_launch("latent_unfold");
+}
+
 ZLM_TRANSLATION_UNIT(latent_attention)

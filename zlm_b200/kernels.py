@@ -701,6 +701,31 @@ class CudaKernels:
                    c_int(block_table.stride(0) if dkv is not None else 0), self._p(pool if dkv is not None else None),
                    c_int(T), c_int(heads), c_int(dim), c_int(rot_dim), c_int(kv_rank), self._stream())
 
+    def latent_gather(self, rec: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, token_pos: torch.Tensor,
+                      token_slot: torch.Tensor) -> None:
+        """rec[t] = the record of token t (position token_pos[t] of slot token_slot[t]) from the paged ``pool``."""
+        T, R = rec.shape
+        assert rec.is_contiguous() and pool.is_contiguous() and rec.dtype == pool.dtype
+        assert tuple(pool.shape[1:]) == (PAGE_TOKENS, R) and block_table.dtype == torch.int32
+        self._call("zlm_latent_gather", self._p(rec), self._p(pool), self._p(block_table), c_int(block_table.stride(0)),
+                   self._p(token_pos), self._p(token_slot), c_int(_dt(rec)), c_int(T), c_int(R), self._stream())
+
+    def latent_unfold(self, spool: torch.Tensor, stable: torch.Tensor, kv: torch.Tensor, rec: torch.Tensor,
+                      token_pos: torch.Tensor, token_seq: torch.Tensor, heads: int, dim: int, rot_dim: int, v_dim: int,
+                      kv_rank: int) -> None:
+        """Per-head keys and values of the step's tokens into a pool of the attention kernels' layout
+        [pages, 2, heads, PAGE_TOKENS, dim + rot_dim]: K = [kv[t, h*dim : (h+1)*dim] | rec[t, kv_rank:]],
+        V = [kv[t, heads*dim + h*v_dim : ...] | 0]; ``stable`` [sequences of the step, pages] names the pages."""
+        T = kv.shape[0]
+        hd = dim + rot_dim
+        assert kv.shape == (T, heads * (dim + v_dim)) and kv.stride(1) == 1 and rec.shape[0] == T and rec.stride(1) == 1
+        assert spool.is_contiguous() and tuple(spool.shape[1:]) == (2, heads, PAGE_TOKENS, hd) and spool.dtype == kv.dtype
+        assert stable.dtype == torch.int32 and stable.dim() == 2
+        self._call("zlm_latent_unfold", self._p(spool), self._p(stable), c_int(stable.stride(0)), self._p(kv),
+                   c_int(kv.stride(0)), self._p(rec), c_int(rec.stride(0)), self._p(token_pos), self._p(token_seq),
+                   c_int(_dt(kv)), c_int(T), c_int(heads), c_int(dim), c_int(rot_dim), c_int(v_dim), c_int(kv_rank),
+                   self._stream())
+
     def head_linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, impl: Optional[str] = None) -> None:
         """out[t, h, :] = w[h] @ x[t, h, :] for per-head matrices w [heads, N, K]; x [T, heads, K] and out
         [T, heads, N] may be views with any token and head strides (innermost contiguous)."""

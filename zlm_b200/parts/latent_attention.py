@@ -92,6 +92,19 @@ class LatentAttention(Mixer):
         self.w_uv = params.pop("uv").view(H, dv, r).contiguous()
         self.w_o = params.pop("o")
         self.check_products(q=self.w_in, o=self.w_o)
+        # Whole prompts in bfloat16 may run unfolded (see ``_forward_unfolded``): the up-projections as one matrix
+        # [W_uk | W_uv] applied to the step's latents, and W_o with a zero column for every column that pads a
+        # head's values to the keys' width
+        hd = dn + self.dr
+        self.unfoldable = bool(
+            self.w_o.dtype == torch.bfloat16 and hd % 16 == 0 and 16 <= hd <= 192 and dv <= hd and r % 8 == 0
+            and self.R % 8 == 0 and (self.Q + (self.R if self.kv_proj else 0)) % 8 == 0
+            and hasattr(self.rt.k, "latent_unfold"))
+        if self.unfoldable:
+            self.w_ukv = torch.cat([self.w_uk_t.transpose(1, 2).reshape(H * dn, r), self.w_uv.reshape(H * dv, r)]).contiguous()
+            pad = torch.zeros(self.hidden, H, hd, dtype=self.w_o.dtype, device=self.w_o.device)
+            pad[:, :, :dv] = self.w_o.view(self.hidden, H, dv)
+            self.w_o_pad = pad.view(self.hidden, H * hd).contiguous()
 
     def tensors(self) -> Dict[str, torch.Tensor]:
         out = {"q": self.w_in[: self.Q], "o": self.w_o,
@@ -103,6 +116,8 @@ class LatentAttention(Mixer):
         return out
 
     # ---- the step -----------------------------------------------------------
+    UNFOLD_FROM = 128        # tokens of a step from which whole prompts run unfolded
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
         rt, k = self.rt, self.rt.k
         T = x.shape[0]
@@ -112,6 +127,10 @@ class LatentAttention(Mixer):
         if cache.writes != self.kv_proj:
             raise ValueError("latent attention: a layer without W_dkv must read another entry's cache, "
                              "and one with W_dkv keeps its own")
+        if (self.unfoldable and T >= self.UNFOLD_FROM and not ctx.is_decode and ctx.h_seq_start
+                and not any(ctx.h_seq_start)):
+            self._forward_unfolded(x, residual, ctx, cache, writes)
+            return
         qd = rt.ws.get("lat.qd", (T, self.Q + (R if writes else 0)), rt.dtype)
         k.linear(qd, x, self.w_in)
         q = qd[:, : self.Q]
@@ -132,3 +151,59 @@ class LatentAttention(Mixer):
         ov = rt.ws.get("lat.ov", (T, H * dv), rt.dtype)
         k.head_linear(ov.view(T, H, dv), ol.view(T, H, r), self.w_uv)
         k.linear(residual, ov, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next
+
+    def _step_pages(self, ctx: StepContext):
+        """Pages for the step's own tokens, sequence after sequence (whole prompts: positions start at 0), as a table
+        [sequences, pages] on the device and their number; made once per step and shared by the layers."""
+        made = ctx.extras.get("latent.step_pages")
+        if made is None:
+            from ..kernels import PAGE_TOKENS
+            need = [(n + PAGE_TOKENS - 1) // PAGE_TOKENS for n in ctx.h_seq_new]
+            table = torch.zeros((ctx.R, max(need)), dtype=torch.int32)
+            at = 0
+            for i, n in enumerate(need):
+                table[i, :n] = torch.arange(at, at + n, dtype=torch.int32)
+                at += n
+            rows = torch.arange(ctx.R, dtype=torch.int32)
+            made = (table.to(self.rt.device), rows.to(self.rt.device), at)
+            ctx.extras["latent.step_pages"] = made
+        return made
+
+    def _forward_unfolded(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, cache, writes: bool) -> None:
+        """Whole prompts: the records go to the cache as always, but the step's attention runs over per-head keys
+        [W_uk_h c | kr] and values W_uv_h c of its own tokens, written out once into a scratch pool of the library's
+        attention layout: (dim + rot_dim + v_dim) instead of (2 kv_rank + rot_dim) multiply-adds for every query, key
+        and head, on the library's flash attention kernels (tcgen05 at a key width of 128)."""
+        import types
+        from ..kernels import PAGE_TOKENS
+        rt, k = self.rt, self.rt.k
+        T = x.shape[0]
+        H, dn, dr, dv, r, R = self.H, self.dn, self.dr, self.dv, self.r, self.R
+        hd = dn + dr
+        qd = rt.ws.get("lat.qd", (T, self.Q + (R if writes else 0)), rt.dtype)
+        k.linear(qd, x, self.w_in)
+        q = qd[:, : self.Q]
+        q3 = q.view(T, H, self.Dq)
+        # rotated query parts in place; the records into their pages
+        k.latent_prep(q, q3[:, :, dn:], qd[:, self.Q:] if writes else None, self.c_norm, self.eps,
+                      self.position.inv_freq, self.position.n_rot, ctx.token_pos, ctx.token_slot,
+                      cache.block_table, cache.pool, H, dn, dr, r)
+        rec = rt.ws.get("lat.rec", (T, R), rt.dtype)
+        k.latent_gather(rec, cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot)
+        kv = rt.ws.get("lat.kv", (T, H * (dn + dv)), rt.dtype)
+        k.linear(kv, rec[:, :r], self.w_ukv)
+        table, rows, pages = self._step_pages(ctx)
+        spool = rt.ws.get("lat.unfolded", (pages, 2, H, PAGE_TOKENS, hd), rt.dtype)
+        # places beyond a sequence's last token are never written and are multiplied by weights of zero: fresh memory
+        # there must hold numbers, so a buffer that has grown is cleared once
+        seen = getattr(rt, "_unfolded_cleared", (0, 0))
+        if seen[0] != spool.data_ptr() or seen[1] < spool.numel():
+            spool.zero_()
+            rt._unfolded_cleared = (spool.data_ptr(), spool.numel())
+        k.latent_unfold(spool, table, kv, rec, ctx.token_pos, ctx.token_seq, H, dn, dr, dv, r)
+        plan = types.SimpleNamespace(is_decode=False, cu_seqlens=ctx.cu_seqlens, seq_slot=rows, seq_start=ctx.seq_start,
+                                     R=ctx.R, max_new=ctx.max_new, max_len=ctx.max_len, scratch=ctx.scratch,
+                                     h_seq_start=ctx.h_seq_start, h_seq_new=ctx.h_seq_new)
+        ao = rt.ws.get("lat.ao", (T, H * hd), rt.dtype)
+        k.attention(ao, q, spool, table, ctx.token_pos, ctx.token_seq, H, H, hd, self.scale, self.window, plan)
+        k.linear(residual, ao, self.w_o_pad, accumulate=True, defer=True)      # a norm reads the stream next

@@ -201,6 +201,13 @@ class ProfilingKernels:
         n = _nbytes(q) + _nbytes(q_rot) + 2 * _nbytes(dkv)
         return self._timed("latent norm+rope+cache_write", n, 0, self.k.latent_prep, q, q_rot, dkv, *args, **kw)
 
+    def latent_gather(self, rec, *args):
+        return self._timed("latent records gathered", 2 * _nbytes(rec), 0, self.k.latent_gather, rec, *args)
+
+    def latent_unfold(self, spool, stable, kv, rec, *args):
+        return self._timed("per-head keys and values written out", 3 * _nbytes(kv), 0, self.k.latent_unfold, spool, stable,
+                           kv, rec, *args)
+
     def head_linear(self, out, x, w):
         T = x.shape[0]
         n = _nbytes(w) + T * x.shape[1] * x.shape[2] * x.element_size() + T * out.shape[1] * out.shape[2] * out.element_size()
