@@ -174,6 +174,14 @@ def test_routed_feed_forward_kernels(dtype, E, top, F, SF):
     assert torch.allclose(wgt.cpu().double(), ww, atol=1e-6)
     if SF:
         assert torch.allclose(gate.cpu().double(), torch.sigmoid(x.double() @ t64["shared.sg"].t())[:, 0], atol=1e-6)
+    # the same choice from logits that a product left in fp32
+    rows = [t["router"]] + ([t["shared.sg"]] if SF else [])
+    logits = (x.double() @ torch.cat(rows).double().t()).float().cuda()
+    idx2, wgt2, gate2 = torch.zeros_like(idx), torch.zeros_like(wgt), torch.zeros_like(gate)
+    k.moe_choose(idx2, wgt2, logits, E, top, gate2 if SF else None)
+    assert torch.equal(idx2, idx) and torch.allclose(wgt2, wgt, atol=1e-6)
+    if SF:
+        assert torch.allclose(gate2, gate, atol=1e-6)
     act = torch.zeros(T, top, F, dtype=DT[dtype], device="cuda")
     w_up = torch.stack([t[f"e{e}.up"] for e in range(E)]).cuda()
     w_down = torch.stack([t[f"e{e}.down"] for e in range(E)]).cuda()

@@ -50,6 +50,45 @@ __device__ __forceinline__ bool rows_vectorise(const TA* a, const TA* b, int K, 
 }
 
 // ---------------------------------------------------------------------------- router
+// one warp chooses for one token from its scores sc[E] (in shared memory; overwritten)
+__device__ __forceinline__ void route_choose(float* sc, int* __restrict__ idx, float* __restrict__ wgt, int t, int lane, int E,
+                                             int top, int score_kind, int renorm) {
+    if (score_kind == 1) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = 0; e < E; ++e) sum += expf(sc[e] - mx);      // one order for all lanes
+        __syncwarp();
+        for (int e = lane; e < E; e += 32) sc[e] = expf(sc[e] - mx) / sum;
+        __syncwarp();
+    }
+    float chosen_sum = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = sc[e];
+            if (v > bv) { bv = v; bi = e; }        // ascending e: ties keep the lower index
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0 && ZLM_CHK(idx + (size_t)t * top + j, 4) && ZLM_CHK(wgt + (size_t)t * top + j, 4)) {
+            idx[(size_t)t * top + j] = bi;
+            wgt[(size_t)t * top + j] = bv;
+            sc[bi] = -INFINITY;
+        }
+        chosen_sum += bv;
+        __syncwarp();
+    }
+    if (renorm && lane == 0)
+        for (int j = 0; j < top; ++j) wgt[(size_t)t * top + j] /= chosen_sum;
+}
+
 #define ROUTE_WARPS 32
 // TOK tokens a block: a warp computes one expert's logit for all of them from one pass over the expert's row
 // (steps of many tokens would otherwise read the router's matrix once per token from L2); then warp j chooses
@@ -106,42 +145,38 @@ moe_route_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restri
     }
     __syncthreads();
     if (warp >= TOK || t0 + warp >= T) return;
-    const int t = t0 + warp;
+    route_choose(sc_all + warp * E, idx, wgt, t0 + warp, lane, E, top, score_kind, renorm);
+}
+
+// The same choice from logits that a product of the library left in fp32 (bf16 steps: the router's matrix, with the
+// shared expert's gate as one more row, goes through the tensor cores like any other product with fp32 sums):
+// logits [T, ld] with E expert columns and, if has_gate, the gate's logit in column E.  One warp per token.
+__global__ void __launch_bounds__(128)
+moe_choose_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restrict__ gate, const float* __restrict__ logits,
+                  int ld, int T, int E, int top, int has_gate, int score_kind, int renorm) {
+    extern __shared__ float sc_all[];           // [4][E]
+    pdl_trigger();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 4 + warp;
+    pdl_wait();
+    if (t >= T) return;
     float* sc = sc_all + warp * E;
-    if (score_kind == 1) {
-        float mx = -INFINITY;
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
-        mx = warp_max(mx);
-        float sum = 0.f;
-        for (int e = 0; e < E; ++e) sum += expf(sc[e] - mx);      // one order for all lanes
-        __syncwarp();
-        for (int e = lane; e < E; e += 32) sc[e] = expf(sc[e] - mx) / sum;
-        __syncwarp();
-    }
-    float chosen_sum = 0.f;
-    for (int j = 0; j < top; ++j) {
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = sc[e];
-            if (v > bv) { bv = v; bi = e; }        // ascending e: ties keep the lower index
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        if (lane == 0 && ZLM_CHK(idx + (size_t)t * top + j, 4) && ZLM_CHK(wgt + (size_t)t * top + j, 4)) {
-            idx[(size_t)t * top + j] = bi;
-            wgt[(size_t)t * top + j] = bv;
-            sc[bi] = -INFINITY;
-        }
-        chosen_sum += bv;
-        __syncwarp();
-    }
-    if (renorm && lane == 0)
-        for (int j = 0; j < top; ++j) wgt[(size_t)t * top + j] /= chosen_sum;
+    const float* z = logits + (size_t)t * ld;
+    for (int e = lane; e < E; e += 32)
+        if (ZLM_CHK(z + e, 4)) sc[e] = score_kind == 0 ? 1.0f / (1.0f + expf(-z[e])) : z[e];
+    if (has_gate && lane == 0 && ZLM_CHK(z + E, 4) && ZLM_CHK(gate + t, 4)) gate[t] = 1.0f / (1.0f + expf(-z[E]));
+    __syncwarp();
+    route_choose(sc, idx, wgt, t, lane, E, top, score_kind, renorm);
+}
+
+extern "C" int zlm_moe_choose(int* idx, float* wgt, float* gate, const float* logits, int ld, int T, int E, int top,
+                              int has_gate, int score_kind, int renorm, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(E > 0 && E <= 2048 && top > 0 && top <= E && ld >= E + (has_gate ? 1 : 0), "moe_choose: experts=%d top=%d ld=%d", E, top, ld);
+    ZLM_REQUIRE(!has_gate || gate, "moe_choose: a shared gate needs a place for its values");
+    zlm_launch(moe_choose_kernel, (T + 3) / 4, 128, (size_t)4 * E * sizeof(float), st, idx, wgt, gate, logits, ld, T, E, top,
+               has_gate, score_kind, renorm);
+    return zlm_check_launch("moe_choose");
 }
 
 template <typename TA>

@@ -809,6 +809,18 @@ class CudaKernels:
                    c_int(x.stride(0)), self._p(w_router), self._p(w_gate), c_int(_dt(x)), c_int(T), c_int(E), c_int(K),
                    c_int(top), c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0), self._stream())
 
+    def moe_choose(self, idx: torch.Tensor, wgt: torch.Tensor, logits: torch.Tensor, experts: int, top: int,
+                   gate: Optional[torch.Tensor] = None, score: str = "sigmoid", renormalize: bool = False) -> None:
+        """``moe_route``'s choice from fp32 logits [T, experts (+ 1)] that a product left (column ``experts`` is the
+        shared expert's gate logit if ``gate`` is given)."""
+        T = logits.shape[0]
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= experts + (1 if gate is not None else 0)
+        assert idx.dtype == torch.int32 and wgt.dtype == torch.float32 and idx.shape == (T, top) and wgt.shape == (T, top)
+        assert idx.is_contiguous() and wgt.is_contiguous()
+        self._call("zlm_moe_choose", self._p(idx), self._p(wgt), self._p(gate), self._p(logits), c_int(logits.stride(0)),
+                   c_int(T), c_int(experts), c_int(top), c_int(1 if gate is not None else 0),
+                   c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0), self._stream())
+
     def moe_up(self, act: torch.Tensor, x: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor,
                scale_input: bool = True) -> None:
         """act[t, j, :] = relu(W_up[idx[t, j]] (wgt[t, j] x[t]))^2 (``scale_input``), or wgt[t, j] * relu(W_up[..] x[t])^2;

@@ -69,6 +69,12 @@ class RoutedExperts(FeedForward):
             self.w_sup, self.w_sdown = params.pop("shared.up"), params.pop("shared.down")
             self.w_sg = params.pop("shared.sg") if self.shared_gate else None
             self.check_products(shared_up=self.w_sup, shared_down=self.w_sdown)
+        # bfloat16: the router's logits (and the shared gate's) as one product of the library with fp32 sums and fp32
+        # output (bf16 operands multiply exactly in fp32); the 32-bit path keeps the FFMA router kernel
+        self.w_route = None
+        if self.w_router.dtype == torch.bfloat16 and self.hidden % 8 == 0 and hasattr(self.rt.k, "moe_choose"):
+            rows = [self.w_router] + ([self.w_sg.reshape(1, self.hidden)] if self.w_sg is not None else [])
+            self.w_route = torch.cat(rows).contiguous()
 
     def tensors(self) -> Dict[str, torch.Tensor]:
         out = {"router": self.w_router}
@@ -86,7 +92,12 @@ class RoutedExperts(FeedForward):
         idx = rt.ws.get("moe.idx", (T, self.top), torch.int32)
         wgt = rt.ws.get("moe.wgt", (T, self.top), torch.float32)
         gate = rt.ws.get("moe.gate", (T,), torch.float32) if self.shared_gate else None
-        k.moe_route(idx, wgt, x, self.w_router, self.top, gate, self.w_sg, self.score, self.renormalize)
+        if self.w_route is not None:
+            logits = rt.ws.get("moe.logits", (T, self.w_route.shape[0]), torch.float32)
+            k.linear(logits, x, self.w_route)
+            k.moe_choose(idx, wgt, logits, self.E, self.top, gate, self.score, self.renormalize)
+        else:
+            k.moe_route(idx, wgt, x, self.w_router, self.top, gate, self.w_sg, self.score, self.renormalize)
         if T > 16 and rt.dtype == torch.bfloat16 and self.F % 8 == 0 and self.hidden % 8 == 0 and hasattr(k, "moe_grouped"):
             # many tokens: pairs sorted by expert, each expert's rows as tiles of one grouped product
             k.moe_grouped(residual, x, self.w_up, self.w_down, idx, wgt, self.scale_input)

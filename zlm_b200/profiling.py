@@ -233,6 +233,9 @@ class ProfilingKernels:
         return self._timed("router", _nbytes(w_router) + T * K * x.element_size(), 2.0 * T * w_router.numel(),
                            self.k.moe_route, idx, wgt, x, w_router, top, *args, **kw)
 
+    def moe_choose(self, idx, wgt, logits, *args, **kw):
+        return self._timed("router choice", _nbytes(logits), 0, self.k.moe_choose, idx, wgt, logits, *args, **kw)
+
     def _experts_read(self, T, top, w):
         return min(T * top, w.shape[0]) * w.shape[1] * w.shape[2] * w.element_size()
 
