@@ -324,7 +324,7 @@ class PrefillPlan:
 @pytest.mark.parametrize("impl", ["mma", None, "tc1", "tc2"])
 @pytest.mark.parametrize("nq,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 48, 24), (5, 5, 80, 0), (8, 1, 128, 100),
                                               (32, 8, 128, 0), (6, 3, 32, 70), (4, 1, 64, 64), (3, 3, 128, 0),
-                                              (4, 2, 128, 17)])
+                                              (4, 2, 128, 17), (3, 3, 192, 0), (4, 2, 144, 40), (2, 1, 176, 0)])
 def test_attention_prefill_kernel(K, nq, nkv, hd, window, impl):
     """Tiles of query tokens over the paged cache: whole prompts, a chunk that
     continues a cached prefix, a single token, tile and page edges; a far key

@@ -17,6 +17,12 @@ The cache record of a token is [c | kr] (``CacheRequest.token_shape``); a layer 
 The step folds the up-projections away from the cached side: q'_h = W_uk_h^T q_h[:dim] makes the
 score q'_h . c + rot(q_h[dim:]) . kr, and sum_j p_j v_h(j) = W_uv_h (sum_j p_j c_j), so attention
 runs over the records as they are: one key/value record per token that all heads read.
+
+Whole prompts in bfloat16 (every sequence of the step starts at 0) may run *unfolded* instead: the step's records are
+gathered, [W_uk | W_uv] is applied to their latents as one product, per-head keys [W_uk_h c | kr] and values
+[W_uv_h c | 0] go to a scratch pool of the library's attention layout, and the library's flash attention serves the
+step: (dim + rot_dim + v_dim) instead of (2 kv_rank + rot_dim) multiply-adds for every query, key and head.  The cache
+receives the same records either way.
 """
 from __future__ import annotations
 
