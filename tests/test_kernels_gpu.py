@@ -361,6 +361,34 @@ def test_attention_prefill_kernel(K, nq, nkv, hd, window, impl):
     assert (got[299, (nq - 1) * hd:].float().cpu() - vfar).abs().max() < 0.05 * vfar.abs().max() + 0.05
 
 
+@pytest.mark.parametrize("nq,nkv,hd,vd,window", [(3, 3, 192, 128, 0), (4, 2, 96, 64, 40), (2, 2, 64, 32, 0), (4, 1, 48, 32, 70),
+                                                 (3, 1, 32, 16, 0)])
+def test_attention_prefill_kernel_with_narrower_values(K, nq, nkv, hd, vd, window):
+    """Values narrower than keys: the value rows' columns from ``vd`` on are padding (here: garbage that must not
+    be read into the result), the output's columns from ``vd`` on are zeros, the rest is the attention over the
+    first ``vd`` value columns."""
+    dt = torch.bfloat16
+    lens, news = [300, 5, 129, 64, 65], [300, 5, 70, 1, 65]
+    pool, table, slots = make_paged(nkv, hd, lens, dt, 62, n_pages=40)
+    starts = [l - n for l, n in zip(lens, news)]
+    pos = torch.tensor([p for s, n in zip(starts, news) for p in range(s, s + n)], dtype=torch.int32)
+    slot = torch.tensor([sl for sl, n in zip(slots, news) for _ in range(n)], dtype=torch.int32)
+    T = pos.numel()
+    q = rnd((T, nq * hd), dt, 63)
+    scale = 1.0 / math.sqrt(hd)
+    clean = pool.clone()
+    clean[:, 1, :, :, vd:] = 0
+    want = torch.empty(T, nq * hd, dtype=dt)
+    PlainKernels().attention(want, q, clean, table, pos, slot, nq, nkv, hd, scale, window)
+    pool[:, 1, :, :, vd:] = float("nan")
+    got = torch.full((T, nq * hd), 7.0, dtype=dt, device="cuda")
+    plan = PrefillPlan(slots, starts, news)
+    plan.attention_impl = "mma"
+    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window, plan, v_dim=vd)
+    close(got, want, dt, atol=3e-2, rtol=3e-2)
+    assert float(got.view(T, nq, hd)[:, :, vd:].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("T,N,K_", [(128, 256, 64), (130, 300, 72), (200, 151, 1000), (128, 8, 64), (1, 40, 24),
                                     (300, 1000, 520), (512, 768, 2048)])
 def test_linear_bf16_tcgen05(K, T, N, K_):

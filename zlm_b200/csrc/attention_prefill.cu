@@ -16,7 +16,9 @@
 #define PRE_WARPS 4
 #define PRE_THREADS (PRE_WARPS * 32)
 
-template <int HD>
+// VD: how many of the HD value columns are used (a multiple of 16; the pool's values are HD wide, columns from VD
+// on are padding that is neither loaded nor multiplied, and the output's columns from VD on are written as zeros)
+template <int HD, int VD>
 __global__ void __launch_bounds__(PRE_THREADS)
 attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bfloat16* __restrict__ q,
                          int q_stride, const __nv_bfloat16* __restrict__ pool,
@@ -25,8 +27,11 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
                          const int* __restrict__ seq_start, int tiles_per_seq, int nq, int nkv,
                          float scale_log2, int window) {
     constexpr int KS = HD / 16;
+    constexpr int VS = VD / 16;
     constexpr int CH = HD / 8;
+    constexpr int VCH = VD / 8;
     constexpr int TILE = ZLM_PAGE * HD;
+    static_assert(VD % 16 == 0 && VD >= 16 && VD <= HD, "value columns");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* Ks = (__nv_bfloat16*)smem_raw;          // [2][TILE]
     __nv_bfloat16* Vs = Ks + 2 * TILE;                     // [2][TILE]
@@ -81,9 +86,9 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
             qf[ks][3] = ok1 ? *(const unsigned*)(q1 + c + 8) : 0u;
         }
     }
-    float o[2 * KS][4];
+    float o[2 * VS][4];
 #pragma unroll
-    for (int i = 0; i < 2 * KS; ++i)
+    for (int i = 0; i < 2 * VS; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
@@ -97,7 +102,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
         for (int id = tid; id < ZLM_PAGE * CH; id += PRE_THREADS) {
             const int rr = id / CH, c = id % CH;
             dec_cp_async16(ks_ + tile_off<HD>(rr, c), kb + rr * HD + c * 8);
-            dec_cp_async16(vs_ + tile_off<HD>(rr, c), vb + rr * HD + c * 8);
+            if (c < VCH) dec_cp_async16(vs_ + tile_off<HD>(rr, c), vb + rr * HD + c * 8);
         }
     };
 
@@ -171,7 +176,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
         l0 = l0 * a0 + ps0;
         l1 = l1 * a1 + ps1;
 #pragma unroll
-        for (int i = 0; i < 2 * KS; ++i) {
+        for (int i = 0; i < 2 * VS; ++i) {
             o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1;
         }
 #pragma unroll
@@ -182,7 +187,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
             pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
             pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-            for (int dn = 0; dn < KS; ++dn) {
+            for (int dn = 0; dn < VS; ++dn) {
                 const int mi = lane >> 3;
                 const int row = kk * 16 + (mi & 1) * 8 + (lane & 7);
                 const int chunk = dn * 2 + (mi >> 1);
@@ -203,20 +208,26 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
     __nv_bfloat16* o0 = out + (size_t)(tok0 + row0 + i0) * out_stride + (size_t)head * HD;
     __nv_bfloat16* o1 = out + (size_t)(tok0 + row0 + i1) * out_stride + (size_t)head * HD;
 #pragma unroll
-    for (int i = 0; i < 2 * KS; ++i) {
+    for (int i = 0; i < 2 * VS; ++i) {
         const int d = i * 8 + qd * 2;
         if (ok0) *(unsigned*)(o0 + d) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
         if (ok1) *(unsigned*)(o1 + d) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
     }
+#pragma unroll
+    for (int i = 2 * VS; i < 2 * KS; ++i) {
+        const int d = i * 8 + qd * 2;
+        if (ok0) *(unsigned*)(o0 + d) = 0u;
+        if (ok1) *(unsigned*)(o1 + d) = 0u;
+    }
 }
 
-template <int HD>
+template <int HD, int VD = HD>
 static int launch_prefill(__nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride,
                           const __nv_bfloat16* pool, const int* block_table, int table_stride,
                           const int* cu_seqlens, const int* seq_slot, const int* seq_start, int R, int max_new,
                           int nq, int nkv, float scale, int window, cudaStream_t st) {
     const size_t smem = (size_t)4 * ZLM_PAGE * HD * sizeof(__nv_bfloat16);
-    auto kern = attention_prefill_kernel<HD>;
+    auto kern = attention_prefill_kernel<HD, VD>;
     static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -260,6 +271,33 @@ extern "C" int zlm_attention_prefill(void* out, int out_stride, const void* q, i
     }
 #undef ZLM_PRE_CASE
     ZLM_REQUIRE(false, "attention_prefill: head_dim=%d", hd);
+}
+
+// The same with values narrower than keys: the pool's value rows are hd wide but only their first vd columns are
+// used (the rest is padding); out's columns from vd on are written as zeros.  Built for a few pairs of widths.
+extern "C" int zlm_attention_prefill_vd_supported(int nq, int nkv, int hd, int vd) {
+    if (!(nkv > 0 && nq % nkv == 0)) return 0;
+    return ((hd == 192 && vd == 128) || (hd == 128 && vd == 64) || (hd == 96 && vd == 64) || (hd == 64 && vd == 32) ||
+            (hd == 48 && vd == 32) || (hd == 32 && vd == 16)) ? 1 : 0;
+}
+
+extern "C" int zlm_attention_prefill_vd(void* out, int out_stride, const void* q, int q_stride, const void* pool,
+                                        const int* block_table, int table_stride, const int* cu_seqlens,
+                                        const int* seq_slot, const int* seq_start, int R, int max_new, int nq,
+                                        int nkv, int hd, int vd, float scale, int window, cudaStream_t st) {
+    if (R == 0 || max_new == 0) return ZLM_OK;
+    ZLM_REQUIRE(zlm_attention_prefill_vd_supported(nq, nkv, hd, vd),
+                "attention_prefill: keys of %d with values of %d columns is not a pair this kernel is built for", hd, vd);
+    ZLM_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0),
+                "attention_prefill: q and out must be 4-byte aligned");
+#define ZLM_PRE_VD(H, V)                                                                                           \
+    if (hd == H && vd == V)                                                                                        \
+        return launch_prefill<H, V>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,            \
+                                    (const __nv_bfloat16*)pool, block_table, table_stride, cu_seqlens, seq_slot,   \
+                                    seq_start, R, max_new, nq, nkv, scale, window, st);
+    ZLM_PRE_VD(192, 128) ZLM_PRE_VD(128, 64) ZLM_PRE_VD(96, 64) ZLM_PRE_VD(64, 32) ZLM_PRE_VD(48, 32) ZLM_PRE_VD(32, 16)
+#undef ZLM_PRE_VD
+    ZLM_REQUIRE(false, "attention_prefill: head_dim=%d values=%d", hd, vd);
 }
 
 ZLM_TRANSLATION_UNIT(attention_prefill)

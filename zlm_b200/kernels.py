@@ -614,7 +614,8 @@ class CudaKernels:
 
     def attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
                   token_pos: torch.Tensor, token_slot: torch.Tensor, nq: int, nkv: int, hd: int,
-                  scale: float, window: int, plan=None, len_bucket: Optional[int] = None) -> None:
+                  scale: float, window: int, plan=None, len_bucket: Optional[int] = None,
+                  v_dim: Optional[int] = None) -> None:
         """out[t, h] = softmax(q[t, h] . K * scale) V over the keys [start, pos[t]] of the
         token's slot; q may be a column view of the fused qkv buffer.  ``plan`` is the
         step's context (one token per sequence: the split-KV kernel; whole prompts or
@@ -655,6 +656,14 @@ class CudaKernels:
                            self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R),
                            c_int(plan.max_new), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window),
                            self._stream())
+                return
+            if v_dim is not None and v_dim < hd and self.lib.zlm_attention_prefill_vd_supported(nq, nkv, hd, v_dim):
+                # values narrower than keys (their rows in the pool are padded to the keys' width): the padding is
+                # neither loaded nor multiplied, and out's columns from v_dim on become zeros
+                self._call("zlm_attention_prefill_vd", self._p(out), c_int(out.stride(0)), self._p(q), c_int(q.stride(0)),
+                           self._p(pool), self._p(block_table), c_int(block_table.stride(0)), self._p(plan.cu_seqlens),
+                           self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R), c_int(plan.max_new), c_int(nq),
+                           c_int(nkv), c_int(hd), c_int(v_dim), c_float(scale), c_int(window), self._stream())
                 return
             self._call("zlm_attention_prefill", self._p(out), c_int(out.stride(0)),
                        self._p(q), c_int(q.stride(0)), self._p(pool),

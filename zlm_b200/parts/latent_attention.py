@@ -211,5 +211,6 @@ class LatentAttention(Mixer):
                                      R=ctx.R, max_new=ctx.max_new, max_len=ctx.max_len, scratch=ctx.scratch,
                                      h_seq_start=ctx.h_seq_start, h_seq_new=ctx.h_seq_new)
         ao = rt.ws.get("lat.ao", (T, H * hd), rt.dtype)
-        k.attention(ao, q, spool, table, ctx.token_pos, ctx.token_seq, H, H, hd, self.scale, self.window, plan)
+        k.attention(ao, q, spool, table, ctx.token_pos, ctx.token_seq, H, H, hd, self.scale, self.window, plan,
+                    v_dim=dv)
         k.linear(residual, ao, self.w_o_pad, accumulate=True, defer=True)      # a norm reads the stream next

@@ -181,7 +181,7 @@ class ProfilingKernels:
                            n_rot, token_pos, token_slot, block_table, pool, nq, nkv, hd, write)
 
     def attention(self, out, q, pool, block_table, token_pos, token_slot, nq, nkv, hd, scale, window, plan=None,
-                  len_bucket=None):
+                  len_bucket=None, v_dim=None):
         T, el = q.shape[0], q.element_size()
         keys_read, pairs = 0, 0
         if plan is not None and getattr(plan, "h_seq_start", None):
@@ -193,8 +193,8 @@ class ProfilingKernels:
                     pairs += (p + 1) - (max(0, p + 1 - window) if window else 0)
         n = 2 * T * nq * hd * el + keys_read * 2 * nkv * hd * pool.element_size()
         kind = "attention decode" if (plan is not None and plan.is_decode) else "attention prefill"
-        return self._timed(kind, n, 4.0 * nq * hd * pairs, self.k.attention, out, q, pool, block_table, token_pos,
-                           token_slot, nq, nkv, hd, scale, window, plan, len_bucket=len_bucket)
+        return self._timed(kind, n, 2.0 * nq * (hd + (v_dim or hd)) * pairs, self.k.attention, out, q, pool, block_table,
+                           token_pos, token_slot, nq, nkv, hd, scale, window, plan, len_bucket=len_bucket, v_dim=v_dim)
 
     # latent attention and routed experts
     def latent_prep(self, q, q_rot, dkv, *args, **kw):
