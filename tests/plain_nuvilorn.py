@@ -13,7 +13,7 @@ applied to a column):
   snorm    RMS norm with one gain for the whole row: x * g / sqrt(mean(x^2) + eps)
   mixer    q = W_q h, per head [nope | rope part];  [c_raw | kr_raw] = W_dkv h;
            c = vnorm(c_raw, w_dkv_norm) (gain per coordinate);  kr = rot(kr_raw, position),
-           one rotated key part for all heads;  k_nope = W_uk c and v = W_uv c per head;
+           a rotated key slice that every head uses;  k_nope = W_uk c and v = W_uv c per head;
            score(i, j) = (q_nope_i . k_nope_j + rot(q_rope_i) . kr_j) * scale for j <= i, softmax,
            y = W_o [heads' sum_j p_ij v_j].  A layer with ``kv_from`` = j takes c and kr from
            layer j (as that layer made them) and has no W_dkv of its own.
@@ -75,7 +75,7 @@ def latent_of(h: torch.Tensor, w_dkv: torch.Tensor, w_norm: torch.Tensor, m: Map
 
 def latent_attention(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str, m: Mapping[str, Any],
                      positions: torch.Tensor, c: torch.Tensor, kr: torch.Tensor) -> torch.Tensor:
-    """The mixer's output for the rows h [T, width], given the latents c and rotated key parts
+    """The mixer's output for the rows h [T, width], given the latents c and rotated key slices
     kr of the same T positions (its own or another layer's)."""
     T = h.shape[0]
     H, dn, dr, dv, r = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"])

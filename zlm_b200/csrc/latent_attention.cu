@@ -1,6 +1,6 @@
 // Latent attention: every head's keys and values are projections of one small latent per
 // token, so the cache keeps, per token, the record [c (kv_rank) | kr (rot_dim)]: the normed
-// latent and one rotated key part that all heads share.  With the up-projections folded into
+// latent and a rotated key slice that is the same for every head.  With the up-projections folded into
 // the query and the output,
 //     score_h(i, j) = (q'_h(i) . c_j + rot(qr_h(i)) . kr_j) * scale,   q'_h = W_uk_h^T q_nope_h,
 //     o_h(i) = W_uv_h (sum_j p_h(i, j) c_j),

@@ -72,6 +72,7 @@ moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles
     __syncthreads();
     // a pair's place among its expert's rows is whatever the cursor gives it: a row's result does not depend
     // on its place, and the combine step finds it through inv
+    // (lanes that hold the same expert adding once through their first lane was measured: twice as slow)
     for (int i = threadIdx.x; i < P; i += blockDim.x) {
         if (!ZLM_CHK(idx + i, 4)) continue;
         const int e = min(max(idx[i], 0), E - 1);
@@ -233,6 +234,26 @@ moe_combine_kernel(float* __restrict__ stream, const float* __restrict__ y, cons
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
+    if (N % 4 == 0 && ((uintptr_t)y % 16 == 0) && ((uintptr_t)stream % 16 == 0)) {
+        // four columns a thread; a column's sum runs over the choices in their order either way
+        for (int n = threadIdx.x * 4; n < N; n += blockDim.x * 4) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < top; ++j) {
+                if (!ZLM_CHK(inv + (size_t)t * top + j, 4)) continue;
+                const float* row = y + (size_t)inv[(size_t)t * top + j] * N + n;
+                if (!ZLM_CHK(row, 16)) continue;
+                const float4 v = *(const float4*)row;
+                const float w = wgt ? wgt[(size_t)t * top + j] : 1.0f;
+                sum.x += v.x * w; sum.y += v.y * w; sum.z += v.z * w; sum.w += v.w * w;
+            }
+            float* dst = stream + (size_t)t * N + n;
+            if (!ZLM_CHK(dst, 16)) continue;
+            float4 o = *(float4*)dst;
+            o.x += sum.x; o.y += sum.y; o.z += sum.z; o.w += sum.w;
+            *(float4*)dst = o;
+        }
+        return;
+    }
     for (int n = threadIdx.x; n < N; n += blockDim.x) {
         float sum = 0.f;
         for (int j = 0; j < top; ++j)

@@ -6,7 +6,7 @@ With h the mixer's input, per token:
     q = W_q h                        per head [dim | rot_dim]: a plain part and a rotated part
     [c_raw | kr_raw] = W_dkv h       kv_rank + rot_dim rows
     c  = RMSNorm(c_raw) * w_c        the latent (weight per coordinate)
-    kr = rot(kr_raw, pos)            one rotated key part, shared by all heads
+    kr = rot(kr_raw, pos)            a rotated key slice, the same for every head
     k_h = [W_uk_h c | kr],  v_h = W_uv_h c
     score_h(i, j) = (q_h(i) . k_h(j)) * scale,  j in the window ending at i;  softmax;  y = W_o [heads' outputs]
 
