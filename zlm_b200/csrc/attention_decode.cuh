@@ -16,7 +16,7 @@ __device__ __forceinline__ void attention_decode_item(
     unsigned char* smem_raw, const int tid, const GroupSync gs, const int t, const int kvh, const int split,
     __nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride, const __nv_bfloat16* pool,
     const int* block_table, int table_stride, const int* token_pos, const int* token_slot, int nq, int nkv,
-    float scale_log2, int window, int splits, int per, float* part_o, float* part_ml, int fresh) {
+    float scale_log2, int window, int splits, int per, float* part_o, float* part_ml, int fresh, int sink = 0) {
     constexpr int KS = HD / 16;            // k-steps of Q K^T; pairs of output n-tiles of P V
     constexpr int CH = HD / 8;             // 16-byte chunks per row
     constexpr int TILE = ZLM_PAGE * HD;    // elements of one K or V page of one kv head
@@ -101,6 +101,10 @@ __device__ __forceinline__ void attention_decode_item(
 #pragma unroll
         for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8
+    if (sink && split == 0 && warp == 0) {      // a key of score 0 without a value, counted once per (token, head)
+        m0 = m1 = 0.f;
+        if (qd == 0) l0 = l1 = 1.f;
+    }
 
     for (int p = p_begin; p < p_end; ++p) {
         const int stage = (p - p_begin) & 1;

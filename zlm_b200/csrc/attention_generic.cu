@@ -20,7 +20,7 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
                          int q_stride, const TA* __restrict__ pool,
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ token_pos, const int* __restrict__ token_slot,
-                         int nq, int nkv, int hd, float scale, int window) {
+                         int nq, int nkv, int hd, float scale, int window, int sink) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [hd]
     float* accs = sm + hd;                  // [ATT_WARPS][hd]
@@ -46,6 +46,7 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
     __syncthreads();
 
     float m = -INFINITY, l = 0.f;
+    if (sink && warp == 0) { m = 0.f; l = 1.f; }      // a key of score 0 without a value: one more term in the sum
     float acc[ATT_MAX_PER_LANE];
 #pragma unroll
     for (int r = 0; r < ATT_MAX_PER_LANE; ++r) acc[r] = 0.f;
@@ -121,7 +122,7 @@ extern "C" int zlm_attention_generic(void* out, int out_stride, const void* q, i
                                      int dtype, const void* pool, const int* block_table,
                                      int table_stride, const int* token_pos,
                                      const int* token_slot, int T, int nq, int nkv, int hd,
-                                     float scale, int window, cudaStream_t st) {
+                                     float scale, int window, int sink, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
     ZLM_REQUIRE(hd > 0 && hd <= 32 * ATT_MAX_PER_LANE, "attention: head_dim=%d must be at most %d", hd,
                 32 * ATT_MAX_PER_LANE);
@@ -134,12 +135,12 @@ extern "C" int zlm_attention_generic(void* out, int out_stride, const void* q, i
     if (dtype == ZLM_DTYPE_F32)
         attention_generic_kernel<float><<<grid, ATT_WARPS * 32, smem, st>>>(
             (float*)out, out_stride, (const float*)q, q_stride, (const float*)pool, block_table,
-            table_stride, token_pos, token_slot, nq, nkv, hd, scale, window);
+            table_stride, token_pos, token_slot, nq, nkv, hd, scale, window, sink);
     else if (dtype == ZLM_DTYPE_BF16)
         attention_generic_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, st>>>(
             (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)pool, block_table, table_stride, token_pos, token_slot, nq, nkv,
-            hd, scale, window);
+            hd, scale, window, sink);
     else
         ZLM_REQUIRE(false, "attention: unsupported dtype %d", dtype);
     return zlm_check_launch("attention_generic");

@@ -25,7 +25,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, int tiles_per_seq, int nq, int nkv,
-                         float scale_log2, int window) {
+                         float scale_log2, int window, int sink) {
     constexpr int KS = HD / 16;
     constexpr int VS = VD / 16;
     constexpr int CH = HD / 8;
@@ -92,6 +92,10 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    if (sink) {          // a key of score 0 without a value: one more term in every row's sum
+        m0 = m1 = 0.f;
+        if (qd == 0) l0 = l1 = 1.f;
+    }
 
     auto load_page = [&](int p, int stage) {
         if (!ZLM_CHK(pages + p, 4)) return;
@@ -225,7 +229,7 @@ template <int HD, int VD = HD>
 static int launch_prefill(__nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride,
                           const __nv_bfloat16* pool, const int* block_table, int table_stride,
                           const int* cu_seqlens, const int* seq_slot, const int* seq_start, int R, int max_new,
-                          int nq, int nkv, float scale, int window, cudaStream_t st) {
+                          int nq, int nkv, float scale, int window, int sink, cudaStream_t st) {
     const size_t smem = (size_t)4 * ZLM_PAGE * HD * sizeof(__nv_bfloat16);
     auto kern = attention_prefill_kernel<HD, VD>;
     static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];
@@ -241,7 +245,7 @@ static int launch_prefill(__nv_bfloat16* out, int out_stride, const __nv_bfloat1
     ZLM_REQUIRE((long long)R * tiles < 2147483647LL && nq <= 65535, "attention_prefill: too many tiles");
     dim3 grid(R * tiles, nq);
     kern<<<grid, PRE_THREADS, smem, st>>>(out, out_stride, q, q_stride, pool, block_table, table_stride, cu_seqlens,
-                                         seq_slot, seq_start, tiles, nq, nkv, scale * 1.4426950408889634f, window);
+                                         seq_slot, seq_start, tiles, nq, nkv, scale * 1.4426950408889634f, window, sink);
     return zlm_check_launch("attention_prefill");
 }
 
@@ -254,7 +258,7 @@ extern "C" int zlm_attention_prefill_supported(int nq, int nkv, int hd) {
 extern "C" int zlm_attention_prefill(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                                      const int* block_table, int table_stride, const int* cu_seqlens,
                                      const int* seq_slot, const int* seq_start, int R, int max_new, int nq,
-                                     int nkv, int hd, float scale, int window, cudaStream_t st) {
+                                     int nkv, int hd, float scale, int window, int sink, cudaStream_t st) {
     if (R == 0 || max_new == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_attention_prefill_supported(nq, nkv, hd),
                 "attention_prefill: %d heads over %d kv heads of size %d is not a shape this kernel takes", nq, nkv, hd);
@@ -264,7 +268,7 @@ extern "C" int zlm_attention_prefill(void* out, int out_stride, const void* q, i
     case H:                                                                                                     \
         return launch_prefill<H>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,            \
                                  (const __nv_bfloat16*)pool, block_table, table_stride, cu_seqlens, seq_slot,   \
-                                 seq_start, R, max_new, nq, nkv, scale, window, st);
+                                 seq_start, R, max_new, nq, nkv, scale, window, sink, st);
     switch (hd) {
         ZLM_PRE_CASE(16) ZLM_PRE_CASE(32) ZLM_PRE_CASE(48) ZLM_PRE_CASE(64) ZLM_PRE_CASE(80) ZLM_PRE_CASE(96)
         ZLM_PRE_CASE(112) ZLM_PRE_CASE(128) ZLM_PRE_CASE(144) ZLM_PRE_CASE(160) ZLM_PRE_CASE(176) ZLM_PRE_CASE(192)
@@ -284,7 +288,7 @@ extern "C" int zlm_attention_prefill_vd_supported(int nq, int nkv, int hd, int v
 extern "C" int zlm_attention_prefill_vd(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                                         const int* block_table, int table_stride, const int* cu_seqlens,
                                         const int* seq_slot, const int* seq_start, int R, int max_new, int nq,
-                                        int nkv, int hd, int vd, float scale, int window, cudaStream_t st) {
+                                        int nkv, int hd, int vd, float scale, int window, int sink, cudaStream_t st) {
     if (R == 0 || max_new == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_attention_prefill_vd_supported(nq, nkv, hd, vd),
                 "attention_prefill: keys of %d with values of %d columns is not a pair this kernel is built for", hd, vd);
@@ -294,7 +298,7 @@ extern "C" int zlm_attention_prefill_vd(void* out, int out_stride, const void* q
     if (hd == H && vd == V)                                                                                        \
         return launch_prefill<H, V>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,            \
                                     (const __nv_bfloat16*)pool, block_table, table_stride, cu_seqlens, seq_slot,   \
-                                    seq_start, R, max_new, nq, nkv, scale, window, st);
+                                    seq_start, R, max_new, nq, nkv, scale, window, sink, st);
     ZLM_PRE_VD(192, 128) ZLM_PRE_VD(128, 64) ZLM_PRE_VD(96, 64) ZLM_PRE_VD(64, 32) ZLM_PRE_VD(48, 32) ZLM_PRE_VD(32, 16)
 #undef ZLM_PRE_VD
     ZLM_REQUIRE(false, "attention_prefill: head_dim=%d values=%d", hd, vd);

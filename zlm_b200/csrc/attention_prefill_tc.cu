@@ -98,7 +98,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_start, int R, int tiles_per_seq, int nq, int nkv,
-                            float scale_log2, int window) {
+                            float scale_log2, int window, int sink) {
     constexpr int KST = HPC == 2 ? 1 : 2;                           // stages of keys and of values: what fits beside
     constexpr int VST = HPC == 2 ? 2 : 3;                           // the Q and P tiles (7 tiles of 32 KB in all)
     constexpr unsigned Q_BYTES = FA_BM * FA_HD * 2;                 // two halves of [128][64]
@@ -294,7 +294,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos = start + row0 + i;
         const int lo = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
         const unsigned lane_addr = (unsigned)(lg * 32) << 16;
-        float m_ref = -INFINITY, l = 0.f;
+        // (sink: a key of score 0 without a value, one more term in the row's sum)
+        float m_ref = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
         bool ok = true;
         for (int j = 0; j < NS; ++j) {
             ok = mbar_wait_warp(&s_full[hh], j & 1, abort_flag, 3);
@@ -439,7 +440,7 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
                                         const void* pool, long long pool_pages, const int* block_table,
                                         int table_stride, const int* cu_seqlens, const int* seq_slot,
                                         const int* seq_start, int R, int max_new, int nq, int nkv, int hd,
-                                        float scale, int window, cudaStream_t st) {
+                                        float scale, int window, int sink, cudaStream_t st) {
     if (R == 0 || max_new == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_attention_prefill_tc_supported(nq, nkv, hd, q_stride, out_stride),
                 "attention_prefill_tc: %d heads over %d kv heads of size %d (strides %d, %d) is not a shape this kernel takes",
@@ -473,7 +474,7 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
         }                                                                                                         \
         zlm_launch(attention_prefill_tc_kernel<H>, dim3(R * tiles * (nq / H)), dim3(FA_THREADS(H)), smem, st, mq, mkv,    \
                    (__nv_bfloat16*)out, out_stride, block_table, table_stride, cu_seqlens, seq_slot, seq_start,   \
-                   R, tiles, nq, nkv, scale * 1.4426950408889634f, window);                                       \
+                   R, tiles, nq, nkv, scale * 1.4426950408889634f, window, sink);                                       \
     }
     if (hpc == 2) ZLM_FA_LAUNCH(2)
     else ZLM_FA_LAUNCH(1)

@@ -1,0 +1,217 @@
+// A short causal convolution over time on every channel of a fused q/k/v projection, and what follows it in
+// an attention mixer that has one: per-head unit RMS norm of q and k (no weight), q written out head by head,
+// k and v written to the token's place in the paged cache.  The counterpart, for such a mixer, of the
+// norm / rotation / cache-write kernel of the rotary attention mixer.
+//
+//   y_t[c] = sum_j w[c][j] * u_(t - taps + 1 + j)[c],  j = 0 .. taps-1,  zeros before the sequence's start
+//
+// u are the projected values.  Those of the step's own earlier tokens are read from the projection buffer
+// (a sequence's tokens are neighbours in a step); those of earlier steps come from the sequence's state,
+// [slots][taps-1][channels], whose row taps-2 is the newest.  A second kernel writes the state's new rows
+// after the step (a thread owns one channel of one sequence: it reads all it needs before it writes).
+//
+// Heads are padded to `hdp` columns (zeros) in q_out and in the cache, so that keys of `dim` and values of
+// `vdim` columns share the attention kernels' [K|V][kv head][token][hdp] page layout.
+// Sums (taps, squares) are fp32 in both element types.
+#include "common.cuh"
+
+#define SC_WARPS 4
+#define SC_MAX_TAPS 8
+#define SC_MAX_PER_LANE 16      // head sizes up to 512
+
+template <typename TA>
+__global__ void __launch_bounds__(SC_WARPS * 32)
+conv_norm_write_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __restrict__ proj, int proj_stride,
+                       const TA* __restrict__ conv_w, const TA* __restrict__ state, const int* __restrict__ token_pos,
+                       const int* __restrict__ token_slot, const int* __restrict__ token_seq,
+                       const int* __restrict__ seq_start, const int* __restrict__ cu_seqlens,
+                       const int* __restrict__ block_table, int table_stride, TA* __restrict__ pool, int nq, int nkv,
+                       int dim, int vdim, int hdp, int taps, int norm, float eps) {
+    pdl_trigger();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int unit = blockIdx.y * SC_WARPS + warp;
+    if (unit >= nq + 2 * nkv) return;
+    pdl_wait();
+    if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_slot + t, 4) || !ZLM_CHK(token_seq + t, 4)) return;
+    const int pos = token_pos[t], slot = token_slot[t], r = token_seq[t];
+    if (!ZLM_CHK(seq_start + r, 4) || !ZLM_CHK(cu_seqlens + r, 4)) return;
+    const int i = pos - seq_start[r];             // the token's place among its sequence's tokens of this step
+    const int row0 = cu_seqlens[r];
+    const int C = (nq + nkv) * dim + nkv * vdim;
+    const int kind = unit < nq ? 0 : (unit < nq + nkv ? 1 : 2);
+    const int width = kind == 2 ? vdim : dim;
+    const int c0 = kind == 0 ? unit * dim : (kind == 1 ? nq * dim + (unit - nq) * dim : (nq + nkv) * dim + (unit - nq - nkv) * vdim);
+
+    float val[SC_MAX_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int rr = 0; rr < SC_MAX_PER_LANE; ++rr) {
+        const int e = lane + 32 * rr;
+        val[rr] = 0.f;
+        if (e >= width) continue;
+        const int c = c0 + e;
+        float y = 0.f;
+        for (int j = 0; j < taps; ++j) {
+            const int s = i - (taps - 1) + j;
+            if (pos - (taps - 1) + j < 0) continue;                       // before the sequence's start
+            const TA* up = s >= 0 ? proj + (size_t)(row0 + s) * proj_stride + c
+                                  : state + ((size_t)slot * (taps - 1) + (taps - 1 + s)) * C + c;
+            if (!ZLM_CHK(up, sizeof(TA)) || !ZLM_CHK(conv_w + (size_t)c * taps + j, sizeof(TA))) continue;
+            y = fmaf(to_f32(conv_w[(size_t)c * taps + j]), to_f32(*up), y);
+        }
+        val[rr] = y;
+        ss = fmaf(y, y, ss);
+    }
+    float scale = 1.0f;
+    if (norm && kind != 2) {
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)width + eps);
+    }
+    TA* dst;
+    if (kind == 0) {
+        dst = q_out + (size_t)t * q_out_stride + (size_t)unit * hdp;
+    } else {
+        if (!ZLM_CHK(block_table + (size_t)slot * table_stride + pos / ZLM_PAGE, 4)) return;
+        const int page = block_table[(size_t)slot * table_stride + pos / ZLM_PAGE];
+        const int kvh = kind == 1 ? unit - nq : unit - nq - nkv;
+        dst = pool + (((size_t)page * 2 + (kind - 1)) * nkv + kvh) * ZLM_PAGE * hdp + (size_t)(pos % ZLM_PAGE) * hdp;
+    }
+    if (!ZLM_CHK(dst, (size_t)hdp * sizeof(TA))) return;
+#pragma unroll
+    for (int rr = 0; rr < SC_MAX_PER_LANE; ++rr) {
+        const int e = lane + 32 * rr;
+        if (e < hdp) dst[e] = from_f32<TA>(e < width ? val[rr] * scale : 0.f);
+    }
+}
+
+// state[slot][m] <- the (taps-1) newest projected values of the sequence after this step, m = taps-2 the newest
+template <typename TA>
+__global__ void __launch_bounds__(256)
+conv_state_update_kernel(TA* __restrict__ state, const TA* __restrict__ proj, int proj_stride,
+                         const int* __restrict__ seq_slot, const int* __restrict__ cu_seqlens, int C, int taps) {
+    pdl_trigger();
+    const int r = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    pdl_wait();
+    if (c >= C || !ZLM_CHK(seq_slot + r, 4) || !ZLM_CHK(cu_seqlens + r, 8)) return;
+    const int slot = seq_slot[r], row0 = cu_seqlens[r], n = cu_seqlens[r + 1] - row0;
+    TA keep[SC_MAX_TAPS];
+    for (int m = 0; m < taps - 1; ++m) {
+        const int s = n - (taps - 1) + m;
+        const TA* up = s >= 0 ? proj + (size_t)(row0 + s) * proj_stride + c
+                              : state + ((size_t)slot * (taps - 1) + (taps - 1 + s)) * C + c;
+        keep[m] = ZLM_CHK(up, sizeof(TA)) ? *up : from_f32<TA>(0.f);
+    }
+    for (int m = 0; m < taps - 1; ++m) {
+        TA* p = state + ((size_t)slot * (taps - 1) + m) * C + c;
+        if (ZLM_CHK(p, sizeof(TA))) *p = keep[m];
+    }
+}
+
+template <typename TA>
+static void launch_conv(void* q_out, int q_out_stride, const void* proj, int proj_stride, const void* conv_w, void* state,
+                        const int* token_pos, const int* token_slot, const int* token_seq, const int* seq_start,
+                        const int* cu_seqlens, const int* seq_slot, const int* block_table, int table_stride, void* pool,
+                        int T, int R, int nq, int nkv, int dim, int vdim, int hdp, int taps, int norm, float eps,
+                        cudaStream_t st) {
+    const int units = nq + 2 * nkv;
+    zlm_launch(conv_norm_write_kernel<TA>, dim3(T, (units + SC_WARPS - 1) / SC_WARPS), dim3(SC_WARPS * 32), 0, st,
+               (TA*)q_out, q_out_stride, (const TA*)proj, proj_stride, (const TA*)conv_w, (const TA*)state, token_pos,
+               token_slot, token_seq, seq_start, cu_seqlens, block_table, table_stride, (TA*)pool, nq, nkv, dim, vdim, hdp,
+               taps, norm, eps);
+    if (taps > 1) {
+        const int C = (nq + nkv) * dim + nkv * vdim;
+        zlm_launch(conv_state_update_kernel<TA>, dim3(R, (C + 255) / 256), dim3(256), 0, st, (TA*)state, (const TA*)proj,
+                   proj_stride, seq_slot, cu_seqlens, C, taps);
+    }
+}
+
+// proj [T][proj_stride]: columns [q: nq*dim | k: nkv*dim | v: nkv*vdim | anything]; conv_w [channels][taps] in the same
+// element type; state [slots][taps-1][channels] (unused if taps == 1); q_out [T][q_out_stride] receives nq heads of hdp
+// columns; pool [pages][2][nkv][64][hdp].  norm: q and k heads are divided by their root mean square over dim.
+extern "C" int zlm_conv_norm_write(void* q_out, int q_out_stride, const void* proj, int proj_stride, const void* conv_w,
+                                   void* state, int dtype, const int* token_pos, const int* token_slot,
+                                   const int* token_seq, const int* seq_start, const int* cu_seqlens, const int* seq_slot,
+                                   const int* block_table, int table_stride, void* pool, int T, int R, int nq, int nkv,
+                                   int dim, int vdim, int hdp, int taps, int norm, float eps, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(nq > 0 && nkv > 0 && dim > 0 && vdim > 0 && hdp >= dim && hdp >= vdim && hdp <= 32 * SC_MAX_PER_LANE,
+                "conv_norm_write: heads %d/%d of %d and %d columns padded to %d (at most %d)", nq, nkv, dim, vdim, hdp,
+                32 * SC_MAX_PER_LANE);
+    ZLM_REQUIRE(taps >= 1 && taps <= SC_MAX_TAPS, "conv_norm_write: %d taps (at most %d)", taps, SC_MAX_TAPS);
+    ZLM_REQUIRE(taps == 1 || state, "conv_norm_write: a convolution of %d taps needs the sequences' state", taps);
+    ZLM_REQUIRE(T <= 2147483647 / 2 && R <= 65535 * 1024 && (nq + 2 * nkv + SC_WARPS - 1) / SC_WARPS <= 65535,
+                "conv_norm_write: too many tokens, sequences or heads");
+    if (dtype == ZLM_DTYPE_F32)
+        launch_conv<float>(q_out, q_out_stride, proj, proj_stride, conv_w, state, token_pos, token_slot, token_seq, seq_start,
+                           cu_seqlens, seq_slot, block_table, table_stride, pool, T, R, nq, nkv, dim, vdim, hdp, taps, norm,
+                           eps, st);
+    else if (dtype == ZLM_DTYPE_BF16)
+        launch_conv<__nv_bfloat16>(q_out, q_out_stride, proj, proj_stride, conv_w, state, token_pos, token_slot, token_seq,
+                                   seq_start, cu_seqlens, seq_slot, block_table, table_stride, pool, T, R, nq, nkv, dim, vdim,
+                                   hdp, taps, norm, eps, st);
+    else
+        ZLM_REQUIRE(false, "conv_norm_write: unsupported dtype %d", dtype);
+    return zlm_check_launch("conv_norm_write");
+}
+
+// ---------------------------------------------------------------------------- heads times a gate
+// out[t][h*V + e] = unit_norm?(o[t][h][:V])[e] * act(g[t][h*V + e]): the heads of a mixer's output, each optionally
+// divided by its root mean square (fp32), times sigmoid (act 0) or silu (act 1) of a gate projection, written
+// without the heads' padding.  o may be fp32 whatever the element type (a recurrence's output).
+template <typename TO, typename TA>
+__global__ void __launch_bounds__(SC_WARPS * 32)
+head_gate_kernel(TA* __restrict__ out, int out_stride, const TO* __restrict__ o, int o_stride, int o_head_stride,
+                 const TA* __restrict__ g, int g_stride, int H, int V, int norm, float eps, int act) {
+    pdl_trigger();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y * SC_WARPS + warp;
+    if (h >= H) return;
+    pdl_wait();
+    const TO* op = o + (size_t)t * o_stride + (size_t)h * o_head_stride;
+    const TA* gp = g + (size_t)t * g_stride + (size_t)h * V;
+    TA* dst = out + (size_t)t * out_stride + (size_t)h * V;
+    if (!ZLM_CHK(op, (size_t)V * sizeof(TO)) || !ZLM_CHK(gp, (size_t)V * sizeof(TA)) || !ZLM_CHK(dst, (size_t)V * sizeof(TA)))
+        return;
+    float val[SC_MAX_PER_LANE];
+    float ss = 0.f;
+#pragma unroll
+    for (int rr = 0; rr < SC_MAX_PER_LANE; ++rr) {
+        const int e = lane + 32 * rr;
+        val[rr] = e < V ? to_f32(op[e]) : 0.f;
+        ss = fmaf(val[rr], val[rr], ss);
+    }
+    float scale = 1.0f;
+    if (norm) scale = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
+#pragma unroll
+    for (int rr = 0; rr < SC_MAX_PER_LANE; ++rr) {
+        const int e = lane + 32 * rr;
+        if (e >= V) continue;
+        const float z = to_f32(gp[e]);
+        const float sg = 1.0f / (1.0f + expf(-z));
+        dst[e] = from_f32<TA>(val[rr] * scale * (act == 1 ? z * sg : sg));
+    }
+}
+
+extern "C" int zlm_head_gate(void* out, int out_stride, const void* o, int o_is_f32, int o_stride, int o_head_stride,
+                             const void* g, int g_stride, int dtype, int T, int H, int V, int norm, float eps, int act,
+                             cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(H > 0 && V > 0 && V <= 32 * SC_MAX_PER_LANE && (H + SC_WARPS - 1) / SC_WARPS <= 65535,
+                "head_gate: %d heads of %d columns (at most %d)", H, V, 32 * SC_MAX_PER_LANE);
+    ZLM_REQUIRE(act == 0 || act == 1, "head_gate: activation %d", act);
+    const dim3 grid(T, (H + SC_WARPS - 1) / SC_WARPS), block(SC_WARPS * 32);
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(head_gate_kernel<float, float>, grid, block, 0, st, (float*)out, out_stride, (const float*)o, o_stride,
+                   o_head_stride, (const float*)g, g_stride, H, V, norm, eps, act);
+    else if (dtype == ZLM_DTYPE_BF16 && o_is_f32)
+        zlm_launch(head_gate_kernel<float, __nv_bfloat16>, grid, block, 0, st, (__nv_bfloat16*)out, out_stride,
+                   (const float*)o, o_stride, o_head_stride, (const __nv_bfloat16*)g, g_stride, H, V, norm, eps, act);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(head_gate_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, st, (__nv_bfloat16*)out, out_stride,
+                   (const __nv_bfloat16*)o, o_stride, o_head_stride, (const __nv_bfloat16*)g, g_stride, H, V, norm, eps, act);
+    else
+        ZLM_REQUIRE(false, "head_gate: unsupported dtype %d", dtype);
+    return zlm_check_launch("head_gate");
+}
+
+ZLM_TRANSLATION_UNIT(short_conv)

@@ -615,13 +615,16 @@ class CudaKernels:
     def attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
                   token_pos: torch.Tensor, token_slot: torch.Tensor, nq: int, nkv: int, hd: int,
                   scale: float, window: int, plan=None, len_bucket: Optional[int] = None,
-                  v_dim: Optional[int] = None) -> None:
+                  v_dim: Optional[int] = None, sink: bool = False) -> None:
         """out[t, h] = softmax(q[t, h] . K * scale) V over the keys [start, pos[t]] of the
         token's slot; q may be a column view of the fused qkv buffer.  ``plan`` is the
         step's context (one token per sequence: the split-KV kernel; whole prompts or
         chunks: the flash kernels; none: the generic kernel); ``len_bucket`` is the longest
-        sequence in pages as ``attention_len_bucket`` rounds it (computed if absent)."""
+        sequence in pages as ``attention_len_bucket`` rounds it (computed if absent).  ``sink``: the
+        softmax's denominator is 1 + sum exp(s), as if one more key of score 0 without a value stood
+        in every row."""
         T = q.shape[0]
+        sk = c_int(1 if sink else 0)
         assert out.shape == (T, nq * hd) and q.shape[1] == nq * hd and q.dtype == out.dtype == pool.dtype
         assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
         assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
@@ -642,7 +645,7 @@ class CudaKernels:
                        self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
                        c_int(nkv), c_int(hd), c_float(scale), c_int(window), c_int(splits), c_int(per),
                        self._p(part_o), self._p(part_ml), c_int(max(1, int(getattr(plan, "max_new", 1) or 1))),
-                       self._stream())
+                       sk, self._stream())
             return
         if (plan is not None and not plan.is_decode and q.dtype == torch.bfloat16
                 and getattr(plan, "cu_seqlens", None) is not None
@@ -655,7 +658,7 @@ class CudaKernels:
                            c_int(block_table.stride(0)), self._p(plan.cu_seqlens),
                            self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R),
                            c_int(plan.max_new), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window),
-                           self._stream())
+                           sk, self._stream())
                 return
             if v_dim is not None and v_dim < hd and self.lib.zlm_attention_prefill_vd_supported(nq, nkv, hd, v_dim):
                 # values narrower than keys (their rows in the pool are padded to the keys' width): the padding is
@@ -663,20 +666,102 @@ class CudaKernels:
                 self._call("zlm_attention_prefill_vd", self._p(out), c_int(out.stride(0)), self._p(q), c_int(q.stride(0)),
                            self._p(pool), self._p(block_table), c_int(block_table.stride(0)), self._p(plan.cu_seqlens),
                            self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R), c_int(plan.max_new), c_int(nq),
-                           c_int(nkv), c_int(hd), c_int(v_dim), c_float(scale), c_int(window), self._stream())
+                           c_int(nkv), c_int(hd), c_int(v_dim), c_float(scale), c_int(window), sk, self._stream())
                 return
             self._call("zlm_attention_prefill", self._p(out), c_int(out.stride(0)),
                        self._p(q), c_int(q.stride(0)), self._p(pool),
                        self._p(block_table), c_int(block_table.stride(0)),
                        self._p(plan.cu_seqlens), self._p(plan.seq_slot),
                        self._p(plan.seq_start), c_int(plan.R), c_int(plan.max_new), c_int(nq),
-                       c_int(nkv), c_int(hd), c_float(scale), c_int(window), self._stream())
+                       c_int(nkv), c_int(hd), c_float(scale), c_int(window), sk, self._stream())
             return
         self._call("zlm_attention_generic", self._p(out), c_int(out.stride(0)),
                    self._p(q), c_int(q.stride(0)), c_int(_dt(q)), self._p(pool),
                    self._p(block_table), c_int(block_table.stride(0)),
                    self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
-                   c_int(nkv), c_int(hd), c_float(scale), c_int(window), self._stream())
+                   c_int(nkv), c_int(hd), c_float(scale), c_int(window), sk, self._stream())
+
+    # -- short convolution, retention, gated heads (see csrc/short_conv.cu, csrc/retention.cu) --------------
+    def conv_norm_write(self, q_out: torch.Tensor, proj: torch.Tensor, conv_w: torch.Tensor, state: Optional[torch.Tensor],
+                        plan, block_table: torch.Tensor, pool: torch.Tensor, nq: int, nkv: int, dim: int, vdim: int,
+                        taps: int, norm: bool, eps: float) -> None:
+        """On the fused projection ``proj`` [T, >= channels] (columns [q: nq*dim | k: nkv*dim | v: nkv*vdim | ...]): a
+        causal convolution of ``taps`` taps over time on every channel (``conv_w`` [channels, taps]; the values before a
+        step's first token come from ``state`` [slots, taps-1, channels], which is brought up to date afterwards), then
+        q and k heads divided by their root mean square over ``dim`` (``norm``); q goes to ``q_out`` [T, nq*hdp], k and v
+        to the token's place in the paged ``pool`` [pages, 2, nkv, PAGE_TOKENS, hdp], heads padded with zeros to hdp."""
+        T = proj.shape[0]
+        hdp = pool.shape[-1]
+        C = (nq + nkv) * dim + nkv * vdim
+        assert proj.shape[1] >= C and proj.stride(1) == 1 and conv_w.shape == (C, taps) and conv_w.is_contiguous()
+        assert q_out.shape == (T, nq * hdp) and q_out.stride(1) == 1 and pool.is_contiguous()
+        assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hdp) and block_table.dtype == torch.int32
+        assert proj.dtype == conv_w.dtype == q_out.dtype == pool.dtype
+        if taps > 1:
+            assert state is not None and tuple(state.shape[1:]) == (taps - 1, C) and state.is_contiguous() and state.dtype == proj.dtype
+        self._call("zlm_conv_norm_write", self._p(q_out), c_int(q_out.stride(0)), self._p(proj), c_int(proj.stride(0)),
+                   self._p(conv_w), self._p(state if taps > 1 else None), c_int(_dt(proj)), self._p(plan.token_pos),
+                   self._p(plan.token_slot), self._p(plan.token_seq), self._p(plan.seq_start), self._p(plan.cu_seqlens),
+                   self._p(plan.seq_slot), self._p(block_table), c_int(block_table.stride(0)), self._p(pool), c_int(T),
+                   c_int(plan.R), c_int(nq), c_int(nkv), c_int(dim), c_int(vdim), c_int(hdp), c_int(taps),
+                   c_int(1 if norm else 0), c_float(eps), self._stream())
+
+    def head_gate(self, out: torch.Tensor, o: torch.Tensor, g: torch.Tensor, heads: int, v_dim: int, norm: bool,
+                  eps: float, act: str) -> None:
+        """out[t, h*v_dim + e] = o[t, h, e] * act(g[t, h*v_dim + e]) for e < v_dim; with ``norm`` every head of o is first
+        divided by its root mean square (fp32).  o [T, heads, >= v_dim] may be fp32 whatever the compute dtype and may be
+        a view with padded heads; act is "sigmoid" or "silu"; out [T, heads*v_dim] has no padding."""
+        T = o.shape[0]
+        assert o.dim() == 3 and o.shape[1] == heads and o.shape[2] >= v_dim and o.stride(2) == 1
+        assert out.shape == (T, heads * v_dim) and out.stride(1) == 1 and g.shape == (T, heads * v_dim) and g.stride(1) == 1
+        assert out.dtype == g.dtype and o.dtype in (out.dtype, torch.float32)
+        self._call("zlm_head_gate", self._p(out), c_int(out.stride(0)), self._p(o), c_int(1 if o.dtype == torch.float32 else 0),
+                   c_int(o.stride(0)), c_int(o.stride(1)), self._p(g), c_int(g.stride(0)), c_int(_dt(out)), c_int(T),
+                   c_int(heads), c_int(v_dim), c_int(1 if norm else 0), c_float(eps), c_int({"sigmoid": 0, "silu": 1}[act]),
+                   self._stream())
+
+    # tokens of a sequence from which a step's retention runs in pieces side by side, and the pieces' length
+    RETENTION_PIECES_FROM = 256
+    RETENTION_PIECE = 64
+
+    def retention(self, o: torch.Tensor, proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
+                  inv_freq: Optional[torch.Tensor], n_rot: int, decay: torch.Tensor, state: torch.Tensor, plan,
+                  heads: int, dim: int, v_dim: int, k_scale: float, pieces: Optional[bool] = None) -> None:
+        """o [T, heads*v_dim] fp32 = S_t^T q_t with S_t = decay_h S_(t-1) + k_t v_t^T per head, q and k rotated (first
+        ``n_rot`` coordinates of a head, halves against each other, by pos * inv_freq) and k scaled by ``k_scale``; q, k,
+        v are columns of ``proj`` from q_off, k_off, v_off on; ``state`` [slots, heads, dim, v_dim] fp32 holds S between
+        steps.  Long prompts run in pieces side by side (``pieces`` forces or forbids that)."""
+        T = proj.shape[0]
+        assert o.shape == (T, heads * v_dim) and o.dtype == torch.float32 and o.is_contiguous() and proj.stride(1) == 1
+        assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dim, v_dim) and state.is_contiguous()
+        assert decay.dtype == torch.float32 and decay.numel() == heads
+        if inv_freq is not None and n_rot:
+            assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot
+        else:
+            n_rot = 0
+        head = (self._p(o), self._p(proj), c_int(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), c_int(_dt(proj)),
+                self._p(inv_freq if n_rot else None), c_int(n_rot), self._p(decay), self._p(state), self._p(plan.cu_seqlens),
+                self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R))
+        if pieces is None:
+            pieces = plan.max_new >= self.RETENTION_PIECES_FROM
+        if pieces:
+            # the pieces of every sequence, listed on the host (a step's sequences and their lengths are known there)
+            L = self.RETENTION_PIECE
+            p_seq, p_first, s_p0 = [], [], [0]
+            for r, n in enumerate(plan.h_seq_new):
+                for f in range(0, n, L):
+                    p_seq.append(r)
+                    p_first.append(f)
+                s_p0.append(len(p_seq))
+            P = len(p_seq)
+            ints = plan.scratch("retention.pieces", (2 * P + len(s_p0),), torch.int32)
+            ints.copy_(torch.tensor(p_seq + p_first + s_p0, dtype=torch.int32), non_blocking=False)
+            part = plan.scratch("retention.part_state", (P * heads * dim * v_dim,), torch.float32)
+            self._call("zlm_retention_parts", *head, self._p(ints[:P]), self._p(ints[P:2 * P]), self._p(ints[2 * P:]),
+                       c_int(P), c_int(L), self._p(part), c_int(heads), c_int(dim), c_int(v_dim), c_float(k_scale),
+                       self._stream())
+            return
+        self._call("zlm_retention", *head, c_int(heads), c_int(dim), c_int(v_dim), c_float(k_scale), self._stream())
 
     # -- latent attention (see csrc/latent_attention.cu) --------------------
     def latent_prep(self, q: torch.Tensor, q_rot: torch.Tensor, dkv: Optional[torch.Tensor],
@@ -802,10 +887,13 @@ class CudaKernels:
     # -- routed experts (see csrc/moe.cu) -------------------------------------
     def moe_route(self, idx: torch.Tensor, wgt: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, top: int,
                   gate: Optional[torch.Tensor] = None, w_gate: Optional[torch.Tensor] = None,
-                  score: str = "sigmoid", renormalize: bool = False) -> None:
+                  score: str = "sigmoid", renormalize: bool = False, correction: Optional[torch.Tensor] = None,
+                  groups: int = 1, keep: int = 1, weight_scale: float = 1.0) -> None:
         """idx / wgt [T, top]: the experts with the largest scores of W_router x (fp32 logits; ``score``
         "sigmoid" or "softmax") and those scores (divided by their sum if ``renormalize``); gate [T] =
-        sigmoid(w_gate . x) where a shared expert has a gate."""
+        sigmoid(w_gate . x) where a shared expert has a gate.  ``correction`` (fp32 [E]) is added to the scores for the
+        choice only; the experts form ``groups`` equal groups of neighbours of which the ``keep`` with the largest best
+        choice score can be chosen; the weights are the scores times ``weight_scale``."""
         T, K = x.shape
         E = w_router.shape[0]
         assert w_router.shape == (E, K) and w_router.is_contiguous() and w_router.dtype == x.dtype and x.stride(1) == 1
@@ -816,10 +904,18 @@ class CudaKernels:
             assert gate is not None and gate.dtype == torch.float32 and gate.numel() >= T
         self._call("zlm_moe_route", self._p(idx), self._p(wgt), self._p(gate if w_gate is not None else None), self._p(x),
                    c_int(x.stride(0)), self._p(w_router), self._p(w_gate), c_int(_dt(x)), c_int(T), c_int(E), c_int(K),
-                   c_int(top), c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0), self._stream())
+                   c_int(top), c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0),
+                   *self._route_extras(correction, E, groups, keep, weight_scale), self._stream())
+
+    def _route_extras(self, correction, E, groups, keep, weight_scale):
+        if correction is not None:
+            assert correction.dtype == torch.float32 and correction.shape == (E,) and correction.is_contiguous()
+        return self._p(correction), c_int(groups), c_int(keep), c_float(weight_scale)
 
     def moe_choose(self, idx: torch.Tensor, wgt: torch.Tensor, logits: torch.Tensor, experts: int, top: int,
-                   gate: Optional[torch.Tensor] = None, score: str = "sigmoid", renormalize: bool = False) -> None:
+                   gate: Optional[torch.Tensor] = None, score: str = "sigmoid", renormalize: bool = False,
+                   correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1,
+                   weight_scale: float = 1.0) -> None:
         """``moe_route``'s choice from fp32 logits [T, experts (+ 1)] that a product left (column ``experts`` is the
         shared expert's gate logit if ``gate`` is given)."""
         T = logits.shape[0]
@@ -828,28 +924,42 @@ class CudaKernels:
         assert idx.is_contiguous() and wgt.is_contiguous()
         self._call("zlm_moe_choose", self._p(idx), self._p(wgt), self._p(gate), self._p(logits), c_int(logits.stride(0)),
                    c_int(T), c_int(experts), c_int(top), c_int(1 if gate is not None else 0),
-                   c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0), self._stream())
+                   c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0),
+                   *self._route_extras(correction, experts, groups, keep, weight_scale), self._stream())
+
+    _ACT_KINDS = {"relu2": 0, "swiglu": 1, "swiglu_interleaved": 2}
 
     def moe_up(self, act: torch.Tensor, x: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, wgt: torch.Tensor,
-               scale_input: bool = True) -> None:
+               scale_input: bool = True, activation: str = "relu2") -> None:
         """act[t, j, :] = relu(W_up[idx[t, j]] (wgt[t, j] x[t]))^2 (``scale_input``), or wgt[t, j] * relu(W_up[..] x[t])^2;
-        w_up [experts, F, K], act [T, top, F]."""
+        w_up [experts, F, K], act [T, top, F].  ``activation`` "swiglu": w_up is [experts, 2F, K], an expert's gate rows then
+        its up rows, and the activation is silu(gate) * up ("swiglu_interleaved": the rows in groups of 8 gate, 8 up).
+        A choice of an index from ``experts`` on (an identity expert) writes nothing."""
         T, K = x.shape
-        E, F, _ = w_up.shape
         top = idx.shape[1]
-        assert w_up.shape == (E, F, K) and w_up.is_contiguous() and act.shape == (T, top, F) and act.is_contiguous()
+        F = act.shape[2]
+        kind = self._ACT_KINDS[activation]
+        E = w_up.shape[0]
+        assert w_up.shape == (E, F * (2 if kind else 1), K) and w_up.is_contiguous() and act.shape == (T, top, F) and act.is_contiguous()
         assert x.dtype == w_up.dtype == act.dtype and x.stride(1) == 1
         self._call("zlm_moe_up", self._p(act), self._p(x), c_int(x.stride(0)), self._p(w_up), self._p(idx), self._p(wgt),
-                   c_int(_dt(x)), c_int(T), c_int(top), c_int(F), c_int(K), c_int(1 if scale_input else 0), self._stream())
+                   c_int(_dt(x)), c_int(T), c_int(top), c_int(F), c_int(K), c_int(1 if scale_input else 0), c_int(kind),
+                   c_int(E), self._stream())
 
-    def moe_down(self, stream: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor) -> None:
-        """stream[t] += sum_j W_down[idx[t, j]] act[t, j]; w_down [experts, N, F], stream fp32 [T, N]."""
+    def moe_down(self, stream: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor,
+                 identity_input: Optional[torch.Tensor] = None, wgt: Optional[torch.Tensor] = None) -> None:
+        """stream[t] += sum_j W_down[idx[t, j]] act[t, j]; w_down [experts, N, F], stream fp32 [T, N].  With
+        ``identity_input`` x [T, N] and ``wgt``, a choice of an index from ``experts`` on adds wgt[t, j] * x[t]."""
         T, top, F = act.shape
         E, N, _ = w_down.shape
         assert w_down.shape == (E, N, F) and w_down.is_contiguous() and act.is_contiguous() and act.dtype == w_down.dtype
         assert stream.dtype == torch.float32 and stream.shape == (T, N) and stream.is_contiguous()
+        x = identity_input
+        if x is not None:
+            assert x.shape == (T, N) and x.stride(1) == 1 and x.dtype == act.dtype and wgt is not None and wgt.is_contiguous()
         self._call("zlm_moe_down", self._p(stream), self._p(act), self._p(w_down), self._p(idx), c_int(_dt(act)), c_int(T),
-                   c_int(top), c_int(F), c_int(N), self._stream())
+                   c_int(top), c_int(F), c_int(N), c_int(E), self._p(x), c_int(x.stride(0) if x is not None else 0),
+                   self._p(wgt if x is not None else None), self._stream())
 
     def moe_grouped(self, stream: torch.Tensor, x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
                     idx: torch.Tensor, wgt: torch.Tensor, scale_input: bool = True, impl: Optional[str] = None) -> None:

@@ -1,0 +1,98 @@
+"""Grouped-query attention whose q, k and v pass through a short causal convolution over time, with a sink in the
+softmax and a gate on the output.
+
+    q, k, v = conv(W_q x), conv(W_k x), conv(W_v x)     per channel: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros
+                                                        before the sequence's start
+    q, k <- unit_norm per head over head_dim (``qk_norm``; no weight, no rotation: positions do not enter the scores)
+    s_ij = q_i . k_j * scale   for 0 <= i - j < window (window 0: all earlier tokens)
+    p_ij = exp(s_ij) / (1 + sum_j exp(s_ij))            (``sink``: one more term of score 0 that has no value)
+    y = W_o (concat_h(p v) * sigmoid(W_g x))
+
+Query head h reads kv head h // (heads / kv_heads).  Keys are ``head_dim`` wide and values ``v_dim``; in the cache
+both are padded with zeros to one width, so that the pages have the layout the library's attention kernels read.  The
+last taps - 1 projected values of a sequence are its state (``StateRequest``).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..registry import register_mixer
+from .base import CacheRequest, LayerIO, Mixer, ParamSpec, StateRequest, StepContext
+
+
+@register_mixer("conv_attention")
+class ConvAttention(Mixer):
+    reads_input_by_products = True       # x goes into the fused projection and nowhere else
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, conv_taps: int,
+                 scale: float, norm_eps: float, window: int = 0, qk_norm: bool = True, sink: bool = True,
+                 gate: str = "sigmoid"):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"attention: {num_heads} heads over {num_kv_heads} kv heads")
+        if gate not in ("silu", "sigmoid"):
+            raise ValueError(f"attention: gate={gate!r}")
+        self.hidden = int(hidden_size)
+        self.H, self.G, self.D, self.V = int(num_heads), int(num_kv_heads), int(head_dim), int(v_dim)
+        self.taps, self.scale, self.eps = int(conv_taps), float(scale), float(norm_eps)
+        self.window, self.qk_norm, self.sink, self.gate = int(window), bool(qk_norm), bool(sink), gate
+        if self.taps < 1:
+            raise ValueError(f"attention: a convolution of {self.taps} taps")
+        # keys and values share one padded width in the cache (a multiple of 16: what the tensor-core kernels take)
+        self.hdp = (max(self.D, self.V) + 15) // 16 * 16
+        self.C = (self.H + self.G) * self.D + self.G * self.V          # convolved channels: q, k, v
+        self.HV = self.H * self.V
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, G, D, V, K, t = self.H, self.G, self.D, self.V, self.hidden, self.taps
+        return {"q_proj.weight": ParamSpec((H * D, K)), "k_proj.weight": ParamSpec((G * D, K)),
+                "v_proj.weight": ParamSpec((G * V, K)), "g_proj.weight": ParamSpec((self.HV, K)),
+                "q_conv.weight": ParamSpec((H * D, t)), "k_conv.weight": ParamSpec((G * D, t)),
+                "v_conv.weight": ParamSpec((G * V, t)), "o_proj.weight": ParamSpec((K, self.HV))}
+
+    def cache_request(self) -> Optional[CacheRequest]:
+        return CacheRequest(self.G, self.hdp, self.window)
+
+    def state_request(self) -> Optional[StateRequest]:
+        return StateRequest((self.taps - 1, self.C), self.rt.dtype) if self.taps > 1 else None
+
+    def step_key(self, ctx: StepContext):
+        # the decode kernel cuts the longest sequence's pages into parts (as for the rotary attention mixer)
+        if not ctx.is_decode:
+            return None
+        from ..kernels import attention_len_bucket
+        return ("gqa_attention", attention_len_bucket(ctx.max_len))
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        # one fused projection: rows [q | k | v | g]; the convolutions' taps in the same channel order
+        self.w_in = torch.cat([params.pop("q_proj.weight"), params.pop("k_proj.weight"), params.pop("v_proj.weight"),
+                               params.pop("g_proj.weight")], dim=0).contiguous()
+        self.w_conv = torch.cat([params.pop("q_conv.weight"), params.pop("k_conv.weight"), params.pop("v_conv.weight")],
+                                dim=0).contiguous()
+        self.w_o = params.pop("o_proj.weight")
+        self.check_products(in_proj=self.w_in, o_proj=self.w_o)
+
+    def tensors(self) -> Dict[str, torch.Tensor]:
+        a, b, c = self.H * self.D, (self.H + self.G) * self.D, self.C
+        return {"q_proj.weight": self.w_in[:a], "k_proj.weight": self.w_in[a:b], "v_proj.weight": self.w_in[b:c],
+                "g_proj.weight": self.w_in[c:], "q_conv.weight": self.w_conv[:a], "k_conv.weight": self.w_conv[a:b],
+                "v_conv.weight": self.w_conv[b:], "o_proj.weight": self.w_o}
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
+        rt, k = self.rt, self.rt.k
+        T = x.shape[0]
+        cache = io.cache
+        proj = rt.ws.get("conv_attn.proj", (T, self.C + self.HV), rt.dtype)
+        k.linear(proj, x, self.w_in)
+        q = rt.ws.get("conv_attn.q", (T, self.H * self.hdp), rt.dtype)
+        k.conv_norm_write(q, proj, self.w_conv, io.state, ctx, cache.block_table, cache.pool, self.H, self.G, self.D,
+                          self.V, self.taps, self.qk_norm, self.eps)
+        out = rt.ws.get("conv_attn.out", (T, self.H * self.hdp), rt.dtype)
+        key = self.step_key(ctx)
+        k.attention(out, q, cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot, self.H, self.G, self.hdp,
+                    self.scale, self.window, ctx, len_bucket=key[1] if key else None,
+                    v_dim=self.V if self.V < self.hdp else None, sink=self.sink)
+        y = rt.ws.get("conv_attn.gated", (T, self.HV), rt.dtype)
+        k.head_gate(y, out.view(T, self.H, self.hdp), proj[:, self.C:], self.H, self.V, False, self.eps, self.gate)
+        k.linear(residual, y, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next

@@ -10,6 +10,17 @@ shared expert that every token uses.
       + sigmoid(w_sg . h) * shared(h)         the shared expert, if any, with a gate of one number per token
                                               (``shared_gate``; without it the shared expert is added as it is)
 
+Options that other designs use:
+    ``activation="swiglu"``    expert(u) = W_down (silu(W_gate u) * W_up u)     (tensors ``e<i>.gate``, ``e<i>.up``, ``e<i>.down``)
+    ``correction``             a vector (tensor ``correction``) added to the scores for the choice only; the weights
+                               are the scores without it
+    ``groups``, ``keep``       the experts form ``groups`` equal groups of neighbours; a group's mark is its largest
+                               choice score, and only experts of the ``keep`` best groups can be chosen
+    ``route_scale``            multiplies the weights
+    ``identity``               the last ``identity`` of the router's num_experts + identity outputs are experts
+                               without tensors whose output is their input (times the weight); they take part in
+                               the scores, the groups and the choice like any other
+
 The experts' matrices are kept stacked, [experts, ff, hidden] and [experts, hidden, ff], so that a
 kernel reaches an expert by its index; the checkpoint has them one by one (``e<i>.up``, ``e<i>.down``).
 """
@@ -39,7 +50,8 @@ class NoFeedForward(FeedForward):
 class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_ff: int, shared_ff: int = 0,
                  shared_gate: bool = True, score: str = "sigmoid", renormalize: bool = False,
-                 weight_on: str = "input"):
+                 weight_on: str = "input", activation: str = "relu2", correction: bool = False, groups: int = 1,
+                 keep: int = 1, route_scale: float = 1.0, identity: int = 0):
         self.hidden, self.E, self.top, self.F = int(hidden_size), int(num_experts), int(top_k), int(expert_ff)
         self.SF, self.shared_gate = int(shared_ff), bool(shared_gate) and int(shared_ff) > 0
         if not 0 < self.top <= self.E:
@@ -47,10 +59,25 @@ class RoutedExperts(FeedForward):
         if score not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
             raise ValueError(f"routed experts: score={score!r}, weight_on={weight_on!r}")
         self.score, self.renormalize, self.scale_input = score, bool(renormalize), weight_on == "input"
+        if activation not in ("relu2", "swiglu"):
+            raise ValueError(f"routed experts: activation={activation!r}")
+        self.activation, self.has_correction = activation, bool(correction)
+        self.groups, self.keep, self.route_scale, self.identity = int(groups), int(keep), float(route_scale), int(identity)
+        self.routes = self.E + self.identity                       # the router's outputs
+        if self.identity < 0 or self.top > self.routes:
+            raise ValueError(f"routed experts: top_k={self.top} of {self.routes} router outputs, {self.identity} of them identities")
+        if not (1 <= self.keep <= self.groups and self.routes % self.groups == 0
+                and self.keep * (self.routes // self.groups) >= self.top):
+            raise ValueError(f"routed experts: {self.groups} groups over {self.routes} router outputs, {self.keep} kept, "
+                             f"cannot give {self.top} choices")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        s = {"router": ParamSpec((self.E, self.hidden))}
+        s = {"router": ParamSpec((self.routes, self.hidden))}
+        if self.has_correction:
+            s["correction"] = ParamSpec((self.routes,), kind="vector", init="normal")
         for e in range(self.E):
+            if self.activation == "swiglu":
+                s[f"e{e}.gate"] = ParamSpec((self.F, self.hidden))
             s[f"e{e}.up"] = ParamSpec((self.F, self.hidden))
             s[f"e{e}.down"] = ParamSpec((self.hidden, self.F))
         if self.SF:
@@ -62,7 +89,14 @@ class RoutedExperts(FeedForward):
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         self.w_router = params.pop("router")
-        self.w_up = torch.stack([params.pop(f"e{e}.up") for e in range(self.E)]).contiguous()
+        if self.activation == "swiglu":
+            # an expert's first matrix: its gate rows, then its up rows
+            self.w_up = torch.stack([torch.cat([params.pop(f"e{e}.gate"), params.pop(f"e{e}.up")])
+                                     for e in range(self.E)]).contiguous()
+        else:
+            self.w_up = torch.stack([params.pop(f"e{e}.up") for e in range(self.E)]).contiguous()
+        # (the choice adds it to fp32 scores: widened once, exactly)
+        self.correction = params.pop("correction").float().contiguous() if self.has_correction else None
         self.w_down = torch.stack([params.pop(f"e{e}.down") for e in range(self.E)]).contiguous()
         self.w_sup = self.w_sdown = self.w_sg = None
         if self.SF:
@@ -78,8 +112,14 @@ class RoutedExperts(FeedForward):
 
     def tensors(self) -> Dict[str, torch.Tensor]:
         out = {"router": self.w_router}
+        if self.has_correction:
+            out["correction"] = self.correction
         for e in range(self.E):
-            out[f"e{e}.up"], out[f"e{e}.down"] = self.w_up[e], self.w_down[e]
+            if self.activation == "swiglu":
+                out[f"e{e}.gate"], out[f"e{e}.up"] = self.w_up[e, :self.F], self.w_up[e, self.F:]
+            else:
+                out[f"e{e}.up"] = self.w_up[e]
+            out[f"e{e}.down"] = self.w_down[e]
         if self.SF:
             out["shared.up"], out["shared.down"] = self.w_sup, self.w_sdown
             if self.shared_gate:
@@ -95,17 +135,21 @@ class RoutedExperts(FeedForward):
         if self.w_route is not None:
             logits = rt.ws.get("moe.logits", (T, self.w_route.shape[0]), torch.float32)
             k.linear(logits, x, self.w_route)
-            k.moe_choose(idx, wgt, logits, self.E, self.top, gate, self.score, self.renormalize)
+            k.moe_choose(idx, wgt, logits, self.routes, self.top, gate, self.score, self.renormalize, self.correction,
+                         self.groups, self.keep, self.route_scale)
         else:
-            k.moe_route(idx, wgt, x, self.w_router, self.top, gate, self.w_sg, self.score, self.renormalize)
-        if T > 16 and rt.dtype == torch.bfloat16 and self.F % 8 == 0 and self.hidden % 8 == 0 and hasattr(k, "moe_grouped"):
+            k.moe_route(idx, wgt, x, self.w_router, self.top, gate, self.w_sg, self.score, self.renormalize,
+                        self.correction, self.groups, self.keep, self.route_scale)
+        plain = self.activation == "relu2" and not self.identity
+        if (plain and T > 16 and rt.dtype == torch.bfloat16 and self.F % 8 == 0 and self.hidden % 8 == 0
+                and hasattr(k, "moe_grouped")):
             # many tokens: pairs sorted by expert, each expert's rows as tiles of one grouped product
             k.moe_grouped(residual, x, self.w_up, self.w_down, idx, wgt, self.scale_input)
         else:
             # few tokens (and the 32-bit path): every (token, choice) streams its expert's matrices
             act = rt.ws.get("moe.act", (T, self.top, self.F), rt.dtype)
-            k.moe_up(act, x, self.w_up, idx, wgt, self.scale_input)
-            k.moe_down(residual, act, self.w_down, idx)
+            k.moe_up(act, x, self.w_up, idx, wgt, self.scale_input, self.activation)
+            k.moe_down(residual, act, self.w_down, idx, x if self.identity else None, wgt)
         if self.SF:
             u = rt.ws.get("moe.shared_u", (T, self.SF), rt.dtype)
             k.linear(u, x, self.w_sup)

@@ -1,0 +1,79 @@
+"""Retention: linear attention with one fixed decay per head, no softmax and no denominator.
+
+    q = rot(W_q x), k = rot(W_k x) * head_dim^-1/2, v = W_v x     (heads x head_dim, heads x v_dim)
+    S_t = decay_h * S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t         per head; S starts at zero
+    y = W_o (unit_norm(o) * act(W_g x))                            unit_norm per head over v_dim, no weight
+
+The state S [heads, head_dim, v_dim] is fp32 and is what the mixer keeps per sequence (``StateRequest``); it keeps
+no keys or values.  Everything between the projections and the gate (angles, rotated q and k, decay, state, o,
+the heads' norm) is fp32 in both compute dtypes.  The rotation is a registered position encoding whose table of
+frequencies the kernel reads (``rope_half_split``: the first n_rot coordinates of a head, halves against each other).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Mapping, Optional, Sequence
+
+import torch
+
+from ..registry import POSITION_ENCODINGS, lookup, register_mixer
+from .base import LayerIO, Mixer, ParamSpec, StateRequest, StepContext
+
+
+@register_mixer("retention")
+class Retention(Mixer):
+    reads_input_by_products = True       # x goes into the fused projection and nowhere else
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, v_dim: int, decay: Sequence[float],
+                 norm_eps: float, position: Optional[Mapping[str, Any]] = None, gate: str = "silu",
+                 k_scale: Optional[float] = None):
+        self.hidden = int(hidden_size)
+        self.H, self.D, self.V = int(num_heads), int(head_dim), int(v_dim)
+        self.decay_values = [float(d) for d in decay]
+        if len(self.decay_values) != self.H:
+            raise ValueError(f"retention: {len(self.decay_values)} decays for {self.H} heads")
+        if gate not in ("silu", "sigmoid"):
+            raise ValueError(f"retention: gate={gate!r}")
+        self.eps, self.gate = float(norm_eps), gate
+        self.k_scale = float(self.D ** -0.5 if k_scale is None else k_scale)
+        position = dict(position or {"kind": "none"})
+        self.position = lookup(POSITION_ENCODINGS, "position encoding", position.pop("kind"))(**position)
+        if getattr(self.position, "interleaved", False) or not getattr(self.position, "fused", False):
+            raise ValueError("retention: the rotation must be one whose table the kernel reads (rope_half_split or none)")
+        self.QK, self.VV = self.H * self.D, self.H * self.V
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"q_proj.weight": ParamSpec((self.QK, self.hidden)), "k_proj.weight": ParamSpec((self.QK, self.hidden)),
+                "v_proj.weight": ParamSpec((self.VV, self.hidden)), "g_proj.weight": ParamSpec((self.VV, self.hidden)),
+                "o_proj.weight": ParamSpec((self.hidden, self.VV))}
+
+    def state_request(self) -> Optional[StateRequest]:
+        return StateRequest((self.H, self.D, self.V), torch.float32)
+
+    def attach(self, rt) -> None:
+        super().attach(rt)
+        self.position.attach(rt)
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=rt.device)
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        # one fused projection: rows [q | k | v | g]
+        self.w_in = torch.cat([params.pop("q_proj.weight"), params.pop("k_proj.weight"), params.pop("v_proj.weight"),
+                               params.pop("g_proj.weight")], dim=0).contiguous()
+        self.w_o = params.pop("o_proj.weight")
+        self.check_products(in_proj=self.w_in, o_proj=self.w_o)
+
+    def tensors(self) -> Dict[str, torch.Tensor]:
+        a, b = self.QK, 2 * self.QK
+        return {"q_proj.weight": self.w_in[:a], "k_proj.weight": self.w_in[a:b], "v_proj.weight": self.w_in[b:b + self.VV],
+                "g_proj.weight": self.w_in[b + self.VV:], "o_proj.weight": self.w_o}
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
+        rt, k = self.rt, self.rt.k
+        T = x.shape[0]
+        proj = rt.ws.get("retention.proj", (T, 2 * self.QK + 2 * self.VV), rt.dtype)
+        k.linear(proj, x, self.w_in)
+        o = rt.ws.get("retention.o", (T, self.VV), torch.float32)
+        k.retention(o, proj, 0, self.QK, 2 * self.QK, self.position.inv_freq, self.position.n_rot, self.decay, io.state,
+                    ctx, self.H, self.D, self.V, self.k_scale)
+        y = rt.ws.get("retention.gated", (T, self.VV), rt.dtype)
+        k.head_gate(y, o.view(T, self.H, self.V), proj[:, 2 * self.QK + self.VV:], self.H, self.V, True, self.eps, self.gate)
+        k.linear(residual, y, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next
