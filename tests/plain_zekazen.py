@@ -49,8 +49,9 @@ def retention(h, W, m, eps, state=None, start=0):
     T = h.shape[0]
     H, D, V = m["heads"], m["dim"], m["vdim"]
     pos = torch.arange(start, start + T)
-    q = rotate_half((h @ W["q"].T).view(T, H, D), pos, m["rot"]["base"], m["rot"]["dims"])
-    k = rotate_half((h @ W["k"].T).view(T, H, D), pos, m["rot"]["base"], m["rot"]["dims"]) * D ** -0.5
+    base, dims = (m["rot"]["base"], m["rot"]["dims"]) if m.get("rot") else (1.0, 0)
+    q = rotate_half((h @ W["q"].T).view(T, H, D), pos, base, dims)
+    k = rotate_half((h @ W["k"].T).view(T, H, D), pos, base, dims) * D ** -0.5
     v = (h @ W["v"].T).view(T, H, V)
     S = torch.zeros(H, D, V, dtype=F64) if state is None else state.clone()
     decay = torch.tensor(m["decay"], dtype=F64)[:, None, None]
@@ -80,7 +81,7 @@ def conv_attention(h, W, m, eps, cache=None, start=0):
     """m: heads, kv_heads, dim, vdim, conv (taps), scale, mask {size}.  ``cache``: (k [S, G, dim], v [S, G, vdim],
     the three convolutions' histories) of the tokens before ``start``.  Returns (output, new cache)."""
     T = h.shape[0]
-    H, G, D, V = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, D, V = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"]
     hist = (None, None, None) if cache is None else cache[2]
     q, hq = short_conv(h @ W["q"].T, W["q.conv"], hist[0])
     k, hk = short_conv(h @ W["k"].T, W["k.conv"], hist[1])
@@ -91,7 +92,7 @@ def conv_attention(h, W, m, eps, cache=None, start=0):
     if cache is not None:
         k, v = torch.cat([cache[0], k], 0), torch.cat([cache[1], v], 0)
     o = torch.zeros(T, H, V, dtype=F64)
-    window = m["mask"]["size"]
+    window = m["mask"]["size"] if m.get("mask") else start + T          # no mask: every earlier token
     for t in range(T):
         i = start + t
         lo = max(0, i - window + 1)
@@ -105,13 +106,16 @@ def conv_attention(h, W, m, eps, cache=None, start=0):
     return y @ W["o"].T, (k, v, (hq, hk, hv))
 
 
-def route(h, w_router, correction, r):
+def route(h, w_router, correction, r, tilt=None):
     """r: experts, identity, top, scale, groups {count, keep}.  Returns (indices [T, top], weights [T, top],
-    the margin between the last chosen and the first refused choice score, per token)."""
-    n = r["experts"] + r["identity"]
+    the margin between the last chosen and the first refused choice score, per token).  ``tilt`` [T, n], if given,
+    is added to the choice scores (not to the weights): a test's way of asking which outputs hang on close calls."""
+    n = r["experts"] + r.get("identity", 0)
     s = torch.softmax(h @ w_router.T, -1)
     c = s + correction[None, :]
-    count, keep = r["groups"]["count"], r["groups"]["keep"]
+    if tilt is not None:
+        c = c + tilt
+    count, keep = (r["groups"]["count"], r["groups"]["keep"]) if r.get("groups") else (1, 1)
     size = n // count
     best = c.view(-1, count, size).max(-1).values
     kept = torch.zeros_like(best, dtype=torch.bool)
@@ -126,13 +130,13 @@ def route(h, w_router, correction, r):
     gs = torch.sort(best, dim=-1, descending=True).values
     if keep < count:
         margin = torch.minimum(margin, gs[:, keep - 1] - gs[:, keep])
-    return idx, torch.gather(s, 1, idx) * r["scale"], margin
+    return idx, torch.gather(s, 1, idx) * r.get("scale", 1.0), margin
 
 
-def experts(h, W, f):
+def experts(h, W, f, tilt=None):
     """f: expert {ff}, router {...}.  W: router, correction, e<i>.gate / up / down."""
     r = f["router"]
-    idx, wgt, margin = route(h, W["router"], W["correction"], r)
+    idx, wgt, margin = route(h, W["router"], W["correction"], r, tilt)
     y = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(r["top"]):
@@ -149,9 +153,11 @@ def sub(W, prefix):
     return {k[len(prefix):]: v for k, v in W.items() if k.startswith(prefix)}
 
 
-def forward(config, W, tokens, caches=None, start=0):
+def forward(config, W, tokens, caches=None, start=0, tilt=0.0):
     """One sequence: the tokens at positions start .. ; ``caches`` is what an earlier call returned.  Returns
-    (logits [T, vocab], the stream after every layer [layers, T, width], caches, smallest router margin per token)."""
+    (logits [T, vocab], the stream after every layer [layers, T, width], caches, smallest router margin per token).
+    ``tilt``: every router's choice scores are moved by tilt * u, u uniform in [-1, 1] and the same for the same
+    (layer, position, expert) whatever the sign and size of tilt."""
     eps = config["norm"]["eps"]
     x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     new, after = [], []
@@ -167,7 +173,13 @@ def forward(config, W, tokens, caches=None, start=0):
         new.append(c)
         x = x + y
         if layer["mlp"] is not None:
-            y, mg = experts(rms_norm(x, W[p + "norm2"], eps), sub(W, p + "mlp."), layer["mlp"])
+            t = None
+            if tilt:
+                n = layer["mlp"]["router"]["experts"] + layer["mlp"]["router"].get("identity", 0)
+                g = torch.Generator().manual_seed(1000 + i)
+                u = torch.rand(start + x.shape[0], n, generator=g, dtype=F64) * 2 - 1
+                t = tilt * u[start:]
+            y, mg = experts(rms_norm(x, W[p + "norm2"], eps), sub(W, p + "mlp."), layer["mlp"], t)
             margin = torch.minimum(margin, mg)
             x = x + y
         after.append(x)

@@ -54,7 +54,7 @@ class RoutedExperts(FeedForward):
                  keep: int = 1, route_scale: float = 1.0, identity: int = 0):
         self.hidden, self.E, self.top, self.F = int(hidden_size), int(num_experts), int(top_k), int(expert_ff)
         self.SF, self.shared_gate = int(shared_ff), bool(shared_gate) and int(shared_ff) > 0
-        if not 0 < self.top <= self.E:
+        if not 0 < self.top <= self.E + int(identity):
             raise ValueError(f"routed experts: top_k={self.top} of {self.E} experts")
         if score not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
             raise ValueError(f"routed experts: score={score!r}, weight_on={weight_on!r}")
