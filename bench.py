@@ -518,6 +518,20 @@ def _twin(width, heads, kv_heads, inter, layers, vocab):
                 num_key_value_heads=kv_heads, head_dim=128, intermediate_size=inter, vocab_size=vocab)
 
 
+def _zekazen(width, heads, kv_heads, window, experts, identity, top, ff, groups, keep, kinds, vocab):
+    """Heads of 128 (keys, values, retention state 128 x 128 a head), convolutions of 4 taps, gated experts; the twin's
+    feed-forward does the multiply-adds of ``top`` experts (three matrices each, like its own)."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5,
+           "mask": {"size": window}}
+    ret = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, heads - 1)) for h in range(heads)],
+           "rot": {"base": 10000.0, "dims": 128}}
+    moe = {"kind": "moe", "expert": {"ff": ff},
+           "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}}
+    return {"architecture": "Zekazen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": "attention" if k == "a" else "retention", "mixer": dict(att if k == "a" else ret), "mlp": moe}
+                       for k in kinds]}
+
+
 DESIGN_SIZES = {
     # 16 heads of 128 + 64, latents of 512, 64 experts of 1408 (6 a token) and a shared one of 2816
     "lite": (_nuvilorn(2048, 16, 128, 64, 128, 512, 10944, 64, 6, 1408, 2816, 6, 32768), _twin(2048, 16, 4, 7552, 6, 32768)),
@@ -526,12 +540,24 @@ DESIGN_SIZES = {
     # 32 heads, width 4096, 32 experts of 2048 (2 a token) and a shared one of 2048
     "wide": (_nuvilorn(4096, 32, 128, 64, 128, 512, 12288, 32, 2, 2048, 2048, 4, 32768), _twin(4096, 32, 8, 4096, 4, 32768)),
 }
+# Zekazen: attention and retention layers in turn, a window that covers the run (so that its attention does the work
+# of the twin's) or a quarter of it ("small"), 60 + 4 / 30 + 2 router outputs in groups
+ZEKAZEN_SIZES = {
+    # width 2048, 16 heads over 4, 6 layers, 64 router outputs (4 of them identities) in 8 groups of which 4 are kept,
+    # 6 experts of 768 a token
+    "lite": (_zekazen(2048, 16, 4, 4096, 60, 4, 6, 768, 8, 4, "araara", 32768), _twin(2048, 16, 4, 4608, 6, 32768)),
+    # width 1024, 8 heads over 2, a window of 512, 32 router outputs, 4 experts of 512 a token
+    "small": (_zekazen(1024, 8, 2, 512, 30, 2, 4, 512, 4, 2, "araara", 32768), _twin(1024, 8, 2, 2048, 6, 32768)),
+    # width 4096, 32 heads over 8, 4 layers, 2 experts of 2048 a token
+    "wide": (_zekazen(4096, 32, 8, 4096, 30, 2, 2, 2048, 4, 3, "araa", 32768), _twin(4096, 32, 8, 4096, 4, 32768)),
+}
+DESIGNS = {"nuvilorn": ("Nuvilorn", DESIGN_SIZES), "zekazen": ("Zekazen", ZEKAZEN_SIZES)}
 
 
 def design_comparison(args) -> int:
     """Prefill of 2,048 tokens and decode at batch ``--batch`` from 2,048-token prompts, device-timed, for
-    the Nuvilorn design and for its Qwen3-dense twin at each of DESIGN_SIZES, with every operation of both
-    steps (CUDA events; decode operations as graphs of one step's calls); one JSON line."""
+    the design named by ``--design`` and for its Qwen3-dense twin at each of the design's sizes, with every
+    operation of both steps (CUDA events; decode operations as graphs of one step's calls); one JSON line."""
     import torch
     from zlm_b200 import Engine, StepEntry
     from zlm_b200.profiling import profile_engine
@@ -541,11 +567,12 @@ def design_comparison(args) -> int:
     greedy = SamplingParams()
     B, L, steps, warmup = args.batch, PROMPT_LEN, min(args.steps, 64), max(3, args.warmup)
     g = torch.Generator().manual_seed(0)
-    out = {"metric": "prefill and decode tokens/s of Nuvilorn beside Qwen3 dense at equal sizes", "unit": "tokens/s",
+    design, sizes = DESIGNS[args.design]
+    out = {"metric": f"prefill and decode tokens/s of {design} beside Qwen3 dense at equal sizes", "unit": "tokens/s",
            "dtype": "bf16", "data": "synthetic", "batch": B, "prompt_len": L, "peaks": pk, "sizes": {}}
-    for name in ([args.design_size] if args.design_size else list(DESIGN_SIZES)):
+    for name in ([args.design_size] if args.design_size else list(sizes)):
         rec = {}
-        for which, d in zip(("nuvilorn", "qwen3_twin"), DESIGN_SIZES[name]):
+        for which, d in zip((args.design, "qwen3_twin"), sizes[name]):
             cfg = config_from_dict(d)
             eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=B * (L + 256),
                                      max_batch=B, max_seq_len=L + 256, max_step_tokens=B * L)
@@ -630,7 +657,7 @@ def main() -> int:
     ap.add_argument("--no-kernels", action="store_true", help="leave out the per-operation times")
     ap.add_argument("--no-other-sizes", action="store_true",
                     help="leave out the Qwen3-0.6B and Qwen3-32B sizes that the default run adds under points")
-    ap.add_argument("--design", choices=["nuvilorn"],
+    ap.add_argument("--design", choices=sorted(DESIGNS),
                     help="instead of the headline run: that design beside its Qwen3-dense twin at a few layer sizes")
     ap.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None, help="with --design: one of the sizes only")
     args = ap.parse_args()

@@ -1315,7 +1315,8 @@ static int launch_tc_few(void* Y, const void* X, const void* W, int T, int N, in
 // tile_group[tm] (-1: not used in this step), and multiplies that group's matrix, rows
 // [group * N, group * N + N) of W [groups * N, K]; Y [m_tiles * 128, N]; group_of_tile[tm] is tile tm's group.  The persistent single-block
 // form with its tiles' second operand looked up per token tile.
-// mode 0: Y bf16; mode 2: Y fp32; mode 6: Y bf16 = relu(.)^2.
+// mode 0: Y bf16; mode 2: Y fp32; mode 6: Y bf16 = relu(.)^2; mode 3: Y bf16 [.., N / 2] = silu(gate) * up, a group's rows in
+// sixteens of 8 gate rows and the 8 matching up rows.
 extern "C" int zlm_gemm_tc_grouped(void* Y, const void* X, const void* W, const int* group_of_tile, int m_tiles, int groups,
                                    int N, int K, int ldy, int mode, cudaStream_t st) {
     if (m_tiles == 0 || N == 0) return ZLM_OK;
@@ -1324,7 +1325,8 @@ extern "C" int zlm_gemm_tc_grouped(void* Y, const void* X, const void* W, const 
                 m_tiles, groups, N, K);
     ZLM_REQUIRE((long long)groups * N < (1ll << 31), "gemm_tc_grouped: %d groups of %d rows", groups, N);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && group_of_tile, "gemm_tc_grouped: operands must be 16-byte aligned");
-    ZLM_REQUIRE(mode == 0 || mode == 2 || mode == 6, "gemm_tc_grouped: mode %d", mode);
+    ZLM_REQUIRE(mode == 0 || mode == 2 || mode == 3 || mode == 6, "gemm_tc_grouped: mode %d", mode);
+    ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemm_tc_grouped: gated rows come in groups of 16, N=%d", N);
     constexpr int BN = 256, STAGES = 4;
     CUtensorMap mx, mw;
     int rc = make_map(&mx, X, T, K, K, TC_BM);
@@ -1351,6 +1353,7 @@ extern "C" int zlm_gemm_tc_grouped(void* Y, const void* X, const void* W, const 
     }
     if (mode == 0) ZLM_TCG_LAUNCH(0)
     else if (mode == 2) ZLM_TCG_LAUNCH(2)
+    else if (mode == 3) ZLM_TCG_LAUNCH(3)
     else ZLM_TCG_LAUNCH(6)
 #undef ZLM_TCG_LAUNCH
     return zlm_check_launch("gemm_tc_grouped");

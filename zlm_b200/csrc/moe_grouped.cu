@@ -27,7 +27,7 @@ __device__ __forceinline__ void mg_cp_async16(void* smem, const void* gmem, bool
 // One block.  counts and cursors in shared memory (E entries each); tile table: tile -> (expert, first
 // sorted row, rows), expert -1 for the tiles a step does not need.
 __global__ void __launch_bounds__(1024)
-moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles, int padded, int* __restrict__ perm,
+moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles, int padded, int drop, int* __restrict__ perm,
                 int* __restrict__ inv, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                 int* __restrict__ tile_rows) {
     extern __shared__ int sh[];
@@ -42,8 +42,9 @@ moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles
         for (int i = threadIdx.x; i < max_tiles * BM; i += blockDim.x)
             if (ZLM_CHK(perm + i, 4)) perm[i] = -1;
     __syncthreads();
+    // drop: a pair whose index is E or more (an expert without matrices) gets no row; its inv is -1
     for (int i = threadIdx.x; i < P; i += blockDim.x)
-        if (ZLM_CHK(idx + i, 4)) atomicAdd(&count[min(max(idx[i], 0), E - 1)], 1);
+        if (ZLM_CHK(idx + i, 4) && !(drop && idx[i] >= E)) atomicAdd(&count[min(max(idx[i], 0), E - 1)], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int s = 0, t = 0;
@@ -75,6 +76,10 @@ moe_sort_kernel(const int* __restrict__ idx, int P, int E, int BM, int max_tiles
     // (lanes that hold the same expert adding once through their first lane was measured: twice as slow)
     for (int i = threadIdx.x; i < P; i += blockDim.x) {
         if (!ZLM_CHK(idx + i, 4)) continue;
+        if (drop && idx[i] >= E) {
+            if (ZLM_CHK(inv + i, 4)) inv[i] = -1;
+            continue;
+        }
         const int e = min(max(idx[i], 0), E - 1);
         const int place = start[e] + atomicAdd(&count[e], 1);
         if (ZLM_CHK(perm + place, 4) && ZLM_CHK(inv + i, 4)) {
@@ -230,7 +235,9 @@ moe_grouped_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ A, co
 // stream[t, :] += sum_j y[inv[t * top + j], :]; one block per token
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ stream, const float* __restrict__ y, const int* __restrict__ inv,
-                   const float* __restrict__ wgt, int top, int N) {
+                   const float* __restrict__ wgt, int top, int N, const __nv_bfloat16* __restrict__ x = nullptr, int x_stride = 0,
+                   const float* __restrict__ xw = nullptr) {
+    // a pair without a row (inv < 0: an identity expert) adds xw * x[t] instead, if x is given
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -240,6 +247,14 @@ moe_combine_kernel(float* __restrict__ stream, const float* __restrict__ y, cons
             float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int j = 0; j < top; ++j) {
                 if (!ZLM_CHK(inv + (size_t)t * top + j, 4)) continue;
+                if (inv[(size_t)t * top + j] < 0) {
+                    const __nv_bfloat16* xr = x + (size_t)t * x_stride + n;
+                    if (!x || !ZLM_CHK(xr, 8) || !ZLM_CHK(xw + (size_t)t * top + j, 4)) continue;
+                    const float w = xw[(size_t)t * top + j];
+                    sum.x += w * __bfloat162float(xr[0]); sum.y += w * __bfloat162float(xr[1]);
+                    sum.z += w * __bfloat162float(xr[2]); sum.w += w * __bfloat162float(xr[3]);
+                    continue;
+                }
                 const float* row = y + (size_t)inv[(size_t)t * top + j] * N + n;
                 if (!ZLM_CHK(row, 16)) continue;
                 const float4 v = *(const float4*)row;
@@ -256,9 +271,16 @@ moe_combine_kernel(float* __restrict__ stream, const float* __restrict__ y, cons
     }
     for (int n = threadIdx.x; n < N; n += blockDim.x) {
         float sum = 0.f;
-        for (int j = 0; j < top; ++j)
-            if (ZLM_CHK(inv + (size_t)t * top + j, 4) && ZLM_CHK(y + (size_t)inv[(size_t)t * top + j] * N + n, 4))
+        for (int j = 0; j < top; ++j) {
+            if (!ZLM_CHK(inv + (size_t)t * top + j, 4)) continue;
+            if (inv[(size_t)t * top + j] < 0) {
+                if (x && ZLM_CHK(x + (size_t)t * x_stride + n, 2) && ZLM_CHK(xw + (size_t)t * top + j, 4))
+                    sum += xw[(size_t)t * top + j] * __bfloat162float(x[(size_t)t * x_stride + n]);
+                continue;
+            }
+            if (ZLM_CHK(y + (size_t)inv[(size_t)t * top + j] * N + n, 4))
                 sum += y[(size_t)inv[(size_t)t * top + j] * N + n] * (wgt ? wgt[(size_t)t * top + j] : 1.0f);
+        }
         if (ZLM_CHK(stream + (size_t)t * N + n, 4)) stream[(size_t)t * N + n] += sum;
     }
 }
@@ -348,7 +370,7 @@ extern "C" int zlm_moe_grouped(float* stream, const void* x, int x_stride, const
     int* perm = ints;
     int* inv = ints + P;
     int* tiles = ints + 2 * P;
-    zlm_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(3 * E + 2) * sizeof(int), st, idx, P, E, BM, max_tiles, 0, perm,
+    zlm_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(3 * E + 2) * sizeof(int), st, idx, P, E, BM, max_tiles, 0, 0, perm,
                inv, tiles, tiles + max_tiles, tiles + 2 * max_tiles);
     int rc = zlm_check_launch("moe_sort");
     if (rc) return rc;
@@ -365,7 +387,8 @@ extern "C" int zlm_moe_grouped(float* stream, const void* x, int x_stride, const
     else if (BM == 64) ZLM_MG(64, 2, 4);
     else ZLM_MG(128, 2, 4);
 #undef ZLM_MG
-    zlm_launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, stream, (const float*)y, (const int*)inv, (const float*)nullptr, top, K);
+    zlm_launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, stream, (const float*)y, (const int*)inv, (const float*)nullptr, top, K,
+               (const __nv_bfloat16*)nullptr, 0, (const float*)nullptr);
     return zlm_check_launch("moe_combine");
 }
 
@@ -377,7 +400,7 @@ extern "C" int zlm_moe_sort_padded(const int* idx, int P, int E, int max_tiles, 
     int* perm = ints;
     int* inv = ints + (size_t)max_tiles * 128;
     int* tiles = inv + P;
-    zlm_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(3 * E + 2) * sizeof(int), st, idx, P, E, 128, max_tiles, 1, perm,
+    zlm_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(3 * E + 2) * sizeof(int), st, idx, P, E, 128, max_tiles, 1, 1, perm,
                inv, tiles, tiles + max_tiles, tiles + 2 * max_tiles);
     return zlm_check_launch("moe_sort");
 }
@@ -423,11 +446,13 @@ extern "C" int zlm_moe_gather(void* xs, const void* x, int x_stride, const int* 
     return zlm_check_launch("moe_gather");
 }
 
-// stream[t, :] += sum_j (wgt[t, j] or 1) * y[inv[t, j], :]
+// stream[t, :] += sum_j (wgt[t, j] or 1) * y[inv[t, j], :]; a pair with inv < 0 (an identity expert, dropped by the sort)
+// adds xw[t, j] * x[t, :] if x (bf16 [T, x_stride]) is given
 extern "C" int zlm_moe_combine(float* stream, const float* y, const int* inv, const float* wgt, int T, int top, int N,
-                               cudaStream_t st) {
+                               const void* x, int x_stride, const float* xw, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
-    zlm_launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, stream, y, inv, wgt, top, N);
+    ZLM_REQUIRE(!x || xw, "moe_combine: identity experts need their weights");
+    zlm_launch(moe_combine_kernel, dim3(T), dim3(256), 0, st, stream, y, inv, wgt, top, N, (const __nv_bfloat16*)x, x_stride, xw);
     return zlm_check_launch("moe_combine");
 }
 

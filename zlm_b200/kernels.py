@@ -962,23 +962,31 @@ class CudaKernels:
                    self._p(wgt if x is not None else None), self._stream())
 
     def moe_grouped(self, stream: torch.Tensor, x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
-                    idx: torch.Tensor, wgt: torch.Tensor, scale_input: bool = True, impl: Optional[str] = None) -> None:
+                    idx: torch.Tensor, wgt: torch.Tensor, scale_input: bool = True, impl: Optional[str] = None,
+                    activation: str = "relu2", identity: bool = False) -> None:
         """What ``moe_up`` and ``moe_down`` compute, for steps of many tokens (bf16): the (token, choice) pairs
         are sorted by expert on the device and every expert's rows go through its matrices as tiles of one
         grouped tensor-core product, so an expert's weights are read once per tile, not once per token.  Two
         forms (``impl`` forces one): "tc", TMA + tcgen05 on tiles of 128 rows, where an expert gets about half
-        a tile or more; "mma", mma.sync on tiles of 16 to 128 rows, for fewer rows an expert."""
+        a tile or more; "mma", mma.sync on tiles of 16 to 128 rows, for fewer rows an expert.  ``activation``
+        "swiglu_interleaved": w_up is [E, 2F, K], an expert's rows in sixteens of 8 gate and 8 up rows, and the first
+        product's epilogue writes silu(gate) * up ("tc" only).  ``identity``: a choice of an index from E on adds
+        wgt * x[t] and takes no row of any product."""
         T, K = x.shape
-        E, F, _ = w_up.shape
+        E, _, F = w_down.shape
         top = idx.shape[1]
+        gated = activation == "swiglu_interleaved"
+        assert activation in ("relu2", "swiglu_interleaved")
         assert x.dtype == w_up.dtype == w_down.dtype == torch.bfloat16 and x.stride(1) == 1
-        assert w_up.shape == (E, F, K) and w_down.shape == (E, K, F) and w_up.is_contiguous() and w_down.is_contiguous()
+        assert w_up.shape == (E, F * (2 if gated else 1), K) and w_down.shape == (E, K, F) and w_up.is_contiguous() and w_down.is_contiguous()
         assert stream.dtype == torch.float32 and stream.shape == (T, K) and stream.is_contiguous()
         assert idx.shape == (T, top) and wgt.shape == (T, top) and idx.is_contiguous() and wgt.is_contiguous()
         P = T * top
         if impl is None:
             # rows an expert gets on average: from about half a tile of 128 on, the tcgen05 grouped product
-            impl = "tc" if (P >= 64 * E and K % 8 == 0 and F % 8 == 0 and x.stride(0) % 8 == 0) else "mma"
+            impl = "tc" if ((P >= 64 * E or gated or identity) and K % 8 == 0 and F % 8 == 0 and x.stride(0) % 8 == 0) else "mma"
+        if impl != "tc" and (gated or identity):
+            raise KernelError("moe_grouped: gated or identity experts run on the tcgen05 form only (sizes multiples of 8)")
         if impl == "tc":
             # pairs sorted into tiles of 128 rows that start at an expert's first row; the inputs gathered (with the
             # pair's weight, which scales the expert's input) into that order; both products as grouped tcgen05
@@ -994,11 +1002,12 @@ class CudaKernels:
             self._call("zlm_moe_gather", self._p(xs), self._p(x), c_int(x.stride(0)), self._p(perm), self._p(wgt), c_int(rows),
                        c_int(top), c_int(K), c_int(1 if scale_input else 0), self._stream())
             self._call("zlm_gemm_tc_grouped", self._p(act), self._p(xs), self._p(w_up), self._p(table), c_int(tiles), c_int(E),
-                       c_int(F), c_int(K), c_int(F), c_int(6), self._stream())
+                       c_int(2 * F if gated else F), c_int(K), c_int(F), c_int(3 if gated else 6), self._stream())
             self._call("zlm_gemm_tc_grouped", self._p(y), self._p(act), self._p(w_down), self._p(table), c_int(tiles), c_int(E),
                        c_int(K), c_int(F), c_int(K), c_int(2), self._stream())
             self._call("zlm_moe_combine", self._p(stream), self._p(y), self._p(inv), self._p(None if scale_input else wgt),
-                       c_int(T), c_int(top), c_int(K), self._stream())
+                       c_int(T), c_int(top), c_int(K), self._p(x if identity else None), c_int(x.stride(0)),
+                       self._p(wgt if identity else None), self._stream())
             return
         bm = int(self.lib.zlm_moe_grouped_tile_rows(c_int(P), c_int(E)))
         tiles = int(self.lib.zlm_moe_grouped_max_tiles(c_int(P), c_int(E), c_int(bm)))

@@ -89,10 +89,18 @@ class RoutedExperts(FeedForward):
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         self.w_router = params.pop("router")
+        self.up_layout = self.activation
         if self.activation == "swiglu":
-            # an expert's first matrix: its gate rows, then its up rows
-            self.w_up = torch.stack([torch.cat([params.pop(f"e{e}.gate"), params.pop(f"e{e}.up")])
-                                     for e in range(self.E)]).contiguous()
+            gates, ups = [params.pop(f"e{e}.gate") for e in range(self.E)], [params.pop(f"e{e}.up") for e in range(self.E)]
+            if gates[0].dtype == torch.bfloat16 and self.F % 8 == 0 and self.hidden % 8 == 0 and hasattr(self.rt.k, "moe_grouped"):
+                # an expert's first matrix in sixteens of 8 gate rows and the 8 matching up rows: the layout whose
+                # product writes silu(gate) * up from its epilogue
+                from ..kernels import interleave_gate_up
+                self.w_up = torch.stack([interleave_gate_up(g, u) for g, u in zip(gates, ups)]).contiguous()
+                self.up_layout = "swiglu_interleaved"
+            else:
+                # its gate rows, then its up rows
+                self.w_up = torch.stack([torch.cat([g, u]) for g, u in zip(gates, ups)]).contiguous()
         else:
             self.w_up = torch.stack([params.pop(f"e{e}.up") for e in range(self.E)]).contiguous()
         # (the choice adds it to fp32 scores: widened once, exactly)
@@ -115,7 +123,10 @@ class RoutedExperts(FeedForward):
         if self.has_correction:
             out["correction"] = self.correction
         for e in range(self.E):
-            if self.activation == "swiglu":
+            if self.up_layout == "swiglu_interleaved":
+                gu = self.w_up[e].view(self.F // 8, 2, 8, self.hidden)
+                out[f"e{e}.gate"], out[f"e{e}.up"] = gu[:, 0].reshape(self.F, self.hidden), gu[:, 1].reshape(self.F, self.hidden)
+            elif self.activation == "swiglu":
                 out[f"e{e}.gate"], out[f"e{e}.up"] = self.w_up[e, :self.F], self.w_up[e, self.F:]
             else:
                 out[f"e{e}.up"] = self.w_up[e]
@@ -140,15 +151,16 @@ class RoutedExperts(FeedForward):
         else:
             k.moe_route(idx, wgt, x, self.w_router, self.top, gate, self.w_sg, self.score, self.renormalize,
                         self.correction, self.groups, self.keep, self.route_scale)
-        plain = self.activation == "relu2" and not self.identity
-        if (plain and T > 16 and rt.dtype == torch.bfloat16 and self.F % 8 == 0 and self.hidden % 8 == 0
-                and hasattr(k, "moe_grouped")):
+        grouped = self.up_layout == "swiglu_interleaved" or (self.activation == "relu2" and not self.identity)
+        if (grouped and T > 16 and rt.dtype == torch.bfloat16 and self.F % 8 == 0 and self.hidden % 8 == 0
+                and x.stride(0) % 8 == 0 and hasattr(k, "moe_grouped")):
             # many tokens: pairs sorted by expert, each expert's rows as tiles of one grouped product
-            k.moe_grouped(residual, x, self.w_up, self.w_down, idx, wgt, self.scale_input)
+            k.moe_grouped(residual, x, self.w_up, self.w_down, idx, wgt, self.scale_input,
+                          activation=self.up_layout, identity=bool(self.identity))
         else:
             # few tokens (and the 32-bit path): every (token, choice) streams its expert's matrices
             act = rt.ws.get("moe.act", (T, self.top, self.F), rt.dtype)
-            k.moe_up(act, x, self.w_up, idx, wgt, self.scale_input, self.activation)
+            k.moe_up(act, x, self.w_up, idx, wgt, self.scale_input, self.up_layout)
             k.moe_down(residual, act, self.w_down, idx, x if self.identity else None, wgt)
         if self.SF:
             u = rt.ws.get("moe.shared_u", (T, self.SF), rt.dtype)

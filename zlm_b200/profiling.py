@@ -181,7 +181,7 @@ class ProfilingKernels:
                            n_rot, token_pos, token_slot, block_table, pool, nq, nkv, hd, write)
 
     def attention(self, out, q, pool, block_table, token_pos, token_slot, nq, nkv, hd, scale, window, plan=None,
-                  len_bucket=None, v_dim=None):
+                  len_bucket=None, v_dim=None, sink=False):
         T, el = q.shape[0], q.element_size()
         keys_read, pairs = 0, 0
         if plan is not None and getattr(plan, "h_seq_start", None):
@@ -194,7 +194,30 @@ class ProfilingKernels:
         n = 2 * T * nq * hd * el + keys_read * 2 * nkv * hd * pool.element_size()
         kind = "attention decode" if (plan is not None and plan.is_decode) else "attention prefill"
         return self._timed(kind, n, 2.0 * nq * (hd + (v_dim or hd)) * pairs, self.k.attention, out, q, pool, block_table,
-                           token_pos, token_slot, nq, nkv, hd, scale, window, plan, len_bucket=len_bucket, v_dim=v_dim)
+                           token_pos, token_slot, nq, nkv, hd, scale, window, plan, len_bucket=len_bucket, v_dim=v_dim,
+                           sink=sink)
+
+    # short convolution, retention, gated heads
+    def conv_norm_write(self, q_out, proj, conv_w, state, plan, block_table, pool, nq, nkv, dim, vdim, taps, norm, eps):
+        T, el = proj.shape[0], proj.element_size()
+        n = T * ((nq + nkv) * dim + nkv * vdim) * el + _nbytes(q_out) + T * 2 * nkv * pool.shape[-1] * el
+        return self._timed("conv+qk_norm+cache_write", n, 0, self.k.conv_norm_write, q_out, proj, conv_w, state, plan,
+                           block_table, pool, nq, nkv, dim, vdim, taps, norm, eps)
+
+    def head_gate(self, out, o, g, heads, v_dim, norm, eps, act):
+        T = out.shape[0]
+        n = 2 * _nbytes(out) + T * heads * v_dim * o.element_size()
+        return self._timed("heads norm*gate" if norm else "heads*gate", n, 0, self.k.head_gate, out, o, g, heads, v_dim,
+                           norm, eps, act)
+
+    def retention(self, o, proj, q_off, k_off, v_off, inv_freq, n_rot, decay, state, plan, heads, dim, v_dim, k_scale,
+                  pieces=None):
+        T, el = proj.shape[0], proj.element_size()
+        n = T * heads * (2 * dim + v_dim) * el + _nbytes(o) + 2 * plan.R * heads * dim * v_dim * 4
+        kind = "retention decode" if plan.is_decode else "retention prefill"
+        # (fp32 multiply-adds on the ordinary cores, not the tensor cores: state update and read-out)
+        return self._timed(kind, n, 4.0 * T * heads * dim * v_dim, self.k.retention, o, proj, q_off, k_off, v_off, inv_freq,
+                           n_rot, decay, state, plan, heads, dim, v_dim, k_scale, pieces)
 
     # latent attention and routed experts
     def latent_prep(self, q, q_rot, dkv, *args, **kw):
@@ -239,22 +262,26 @@ class ProfilingKernels:
     def _experts_read(self, T, top, w):
         return min(T * top, w.shape[0]) * w.shape[1] * w.shape[2] * w.element_size()
 
-    def moe_up(self, act, x, w_up, idx, wgt, scale_input=True):
+    def moe_up(self, act, x, w_up, idx, wgt, scale_input=True, activation="relu2"):
         T, top = idx.shape
         return self._timed("experts up", self._experts_read(T, top, w_up) + _nbytes(act), 2.0 * T * top * w_up.shape[1] * w_up.shape[2],
-                           self.k.moe_up, act, x, w_up, idx, wgt, scale_input)
+                           self.k.moe_up, act, x, w_up, idx, wgt, scale_input, activation)
 
-    def moe_down(self, stream, act, w_down, idx):
+    def moe_down(self, stream, act, w_down, idx, identity_input=None, wgt=None):
         T, top = idx.shape
         return self._timed("experts down", self._experts_read(T, top, w_down) + _nbytes(act) + 2 * _nbytes(stream),
-                           2.0 * T * top * w_down.shape[1] * w_down.shape[2], self.k.moe_down, stream, act, w_down, idx)
+                           2.0 * T * top * w_down.shape[1] * w_down.shape[2], self.k.moe_down, stream, act, w_down, idx,
+                           identity_input, wgt)
 
-    def moe_grouped(self, stream, x, w_up, w_down, idx, wgt, scale_input=True, impl=None):
+    def moe_grouped(self, stream, x, w_up, w_down, idx, wgt, scale_input=True, impl=None, activation="relu2", identity=False):
         T, top = idx.shape
         n = self._experts_read(T, top, w_up) + self._experts_read(T, top, w_down) + 2 * _nbytes(stream) + T * top * (
             4 * w_up.shape[1] + 8 * w_down.shape[1] + 2 * x.shape[1])
-        return self._timed("experts (sorted, grouped up+down)", n, 4.0 * T * top * w_up.shape[1] * w_up.shape[2],
-                           self.k.moe_grouped, stream, x, w_up, w_down, idx, wgt, scale_input, impl=impl)
+        # (both matrices of every chosen expert: 2 flops a weight and pair)
+        return self._timed("experts (sorted, grouped up+down)", n,
+                           2.0 * T * top * (w_up.shape[1] * w_up.shape[2] + w_down.shape[1] * w_down.shape[2]),
+                           self.k.moe_grouped, stream, x, w_up, w_down, idx, wgt, scale_input, impl=impl,
+                           activation=activation, identity=identity)
 
     def relu2_scale(self, out, u, row_scale=None):
         return self._timed("relu2*gate", _nbytes(out) + _nbytes(u), 0, self.k.relu2_scale, out, u, row_scale)
