@@ -8,9 +8,9 @@
 // q, k, v are columns of one fused projection [T][ld] in the compute element type; everything after the
 // projection (angles, rotated q and k, the decay, the state, o) is fp32 in both element types.
 //
-// The columns of the state are independent: a thread holds DPT rows of one column in registers, the `ds`
-// threads that share a column are neighbouring lanes and add their parts of o by shuffles.  A block takes
-// 128 / ds columns of one head of one sequence and walks the sequence's tokens in order, RT_CHUNK at a time:
+// The columns of the state are independent: a thread holds DPT rows of four columns in registers, the `ds`
+// threads that share the columns are neighbouring lanes and add their parts of o by shuffles.  A block takes
+// 4 * 128 / ds columns of one head of one sequence and walks the sequence's tokens in order, RT_CHUNK at a time:
 // the chunk's rotated q and k and its v columns are staged in shared memory by the whole block.
 //
 // Long prompts, three kernels (retention_parts): the sequence is cut into pieces of `piece` tokens;
@@ -22,38 +22,35 @@
 #include "common.cuh"
 
 #define RT_THREADS 128
-#define RT_CHUNK 16
-
-// rotated coordinate i of a head's vector x (fp32 angle)
-template <typename TA>
-__device__ __forceinline__ float rotated(const TA* __restrict__ x, int i, int n_rot, const float* __restrict__ inv_freq, int pos) {
-    if (i >= n_rot) return to_f32(x[i]);
-    const int half = n_rot >> 1;
-    const int f = i < half ? i : i - half;
-    float sn, cs;
-    sincosf((float)pos * inv_freq[f], &sn, &cs);
-    const float u = to_f32(x[f]), v = to_f32(x[f + half]);
-    return i < half ? u * cs - v * sn : v * cs + u * sn;
-}
+#define RT_CHUNK 64          // tokens staged at a time, at most (a piece of a long prompt)
 
 // MODE 0: the whole recurrence from the sequence's state (reads and writes `state`).
 // MODE 1: a piece from a zero state; its final state goes to part_state [pieces][H][D][V].
 // MODE 2: o += decay^(j+1) * S_before^T q for a piece, S_before from chain [pieces][H][D][V] (the state before piece c).
+//
+// A thread holds a tile of DPT rows x RT_CPT columns of the state, so that a staged q or k value is used for
+// RT_CPT columns and a v value for DPT rows (one column a thread had every thread read all of q and k from shared
+// memory for every token, and the shared-memory pipe, not the arithmetic, set the time).  The `ds` threads that
+// share a tile's columns are neighbouring lanes; their segments of a staged row lie DPT + 4 floats apart, so that
+// their 16-byte reads fall into different banks.
+#define RT_CPT 4
 template <typename TA, int DPT, int MODE>
 __global__ void __launch_bounds__(RT_THREADS)
 retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int q_off, int k_off, int v_off,
                  const float* __restrict__ inv_freq, int n_rot, const float* __restrict__ decay, float* __restrict__ state,
                  const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
-                 const int* __restrict__ piece_seq, const int* __restrict__ piece_first, int piece, int H, int D, int V,
-                 int ds, float k_scale) {
-    extern __shared__ float sm[];
-    float* qs = sm;                          // [RT_CHUNK][D]
-    float* ks = qs + RT_CHUNK * D;           // [RT_CHUNK][D]
-    const int cols = RT_THREADS / ds;
-    float* vs = ks + RT_CHUNK * D;           // [RT_CHUNK][cols]
+                 int maxp, int piece, int H, int D, int V,
+                 int ds, float k_scale, const float* __restrict__ table, int T, int chunk) {
+    extern __shared__ __align__(16) float sm[];
+    const int DP = ds * (DPT + 4);           // a staged row: ds segments of DPT values, 4 floats of padding after each
+    float* qs = sm;                          // [chunk][DP]
+    float* ks = qs + chunk * DP;             // [chunk][DP]
+    const int cols = RT_THREADS / ds * RT_CPT;
+    float* vs = ks + chunk * DP;             // [chunk][cols]
     pdl_launch_dependents();
     const int tid = threadIdx.x, h = blockIdx.y;
-    const int col = blockIdx.x * cols + tid / ds, part = tid % ds;
+    const int grp = tid / ds, part = tid % ds;
+    const int col0 = blockIdx.x * cols + grp * RT_CPT;
     pdl_wait();
     int r, first, n;                          // sequence, first token of this block's run within the step, tokens
     if (MODE == 0) {
@@ -61,34 +58,81 @@ retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int
         first = 0;
         n = cu_seqlens[r + 1] - cu_seqlens[r];
     } else {
-        r = piece_seq[blockIdx.z];
-        first = piece_first[blockIdx.z];
+        // piece blockIdx.z % maxp of sequence blockIdx.z / maxp (maxp: the pieces of the step's longest sequence)
+        r = blockIdx.z / maxp;
+        first = (blockIdx.z % maxp) * piece;
         n = min(piece, cu_seqlens[r + 1] - cu_seqlens[r] - first);
+        if (n <= 0) return;
     }
     const int row0 = cu_seqlens[r] + first, pos0 = seq_start[r] + first;
     const float d = decay[h];
-    float S[DPT];
-    const bool live = col < V;
+    float2 S[DPT][RT_CPT / 2];                // the tile, two neighbouring columns a register pair (packed fp32 arithmetic)
     float* sp = nullptr;
     if (MODE == 0) sp = state + ((size_t)seq_slot[r] * H + h) * D * V;
     else sp = state + ((size_t)blockIdx.z * H + h) * D * V;       // MODE 1: part_state (written); MODE 2: chain (read)
+    const bool v4 = (V & 3) == 0 && col0 + RT_CPT <= V;             // the tile's columns as one 16-byte access
 #pragma unroll
     for (int j = 0; j < DPT; ++j) {
         const int i = part * DPT + j;
-        S[j] = (MODE != 1 && live && i < D && ZLM_CHK(sp + (size_t)i * V + col, 4)) ? sp[(size_t)i * V + col] : 0.f;
+        S[j][0] = S[j][1] = make_float2(0.f, 0.f);
+        if (MODE == 1 || i >= D) continue;
+        const float* src = sp + (size_t)i * V + col0;
+        if (v4 && ZLM_CHK(src, 16)) {
+            const float4 a = *(const float4*)src;
+            S[j][0] = make_float2(a.x, a.y);
+            S[j][1] = make_float2(a.z, a.w);
+        } else {
+            float t[RT_CPT] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < RT_CPT; ++c)
+                if (col0 + c < V && ZLM_CHK(src + c, 4)) t[c] = src[c];
+            S[j][0] = make_float2(t[0], t[1]);
+            S[j][1] = make_float2(t[2], t[3]);
+        }
     }
     float dp = d;                              // MODE 2: decay^(j+1)
-    for (int c0 = 0; c0 < n; c0 += RT_CHUNK) {
-        const int cn = min(RT_CHUNK, n - c0);
+    const int half = n_rot >> 1;
+    for (int c0 = 0; c0 < n; c0 += chunk) {
+        const int cn = min(chunk, n - c0);
         __syncthreads();
-        for (int idx = tid; idx < cn * D; idx += RT_THREADS) {
-            const int tt = idx / D, i = idx % D;
-            const TA* row = proj + (size_t)(row0 + c0 + tt) * ld + (size_t)h * D;
+        // the chunk's q and k, rotated: a thread turns a pair (f, f + half) of a token at a time, so that the pair and
+        // its cosine and sine are read once; the loads of several pairs are in flight together
+#pragma unroll 4
+        for (int idx = tid; idx < cn * half; idx += RT_THREADS) {
+            const int tt = idx / half, f = idx % half;
+            const int rowi = row0 + c0 + tt;
+            const TA* row = proj + (size_t)rowi * ld + (size_t)h * D;
             if (!ZLM_CHK(row + q_off, (size_t)D * sizeof(TA)) || !ZLM_CHK(row + k_off, (size_t)D * sizeof(TA))) continue;
-            qs[tt * D + i] = rotated(row + q_off, i, n_rot, inv_freq, pos0 + c0 + tt);
-            if (MODE != 2) ks[tt * D + i] = rotated(row + k_off, i, n_rot, inv_freq, pos0 + c0 + tt) * k_scale;
+            float sn, cs;
+            if (table) {
+                cs = table[(size_t)f * T + rowi];
+                sn = table[(size_t)(half + f) * T + rowi];
+            } else {
+                sincosf((float)(pos0 + c0 + tt) * inv_freq[f], &sn, &cs);
+            }
+            const int i1 = f + half;
+            const int a0 = tt * DP + (f / DPT) * (DPT + 4) + f % DPT, a1 = tt * DP + (i1 / DPT) * (DPT + 4) + i1 % DPT;
+            const float qu = to_f32(row[q_off + f]), qv = to_f32(row[q_off + i1]);
+            qs[a0] = qu * cs - qv * sn;
+            qs[a1] = qv * cs + qu * sn;
+            if (MODE != 2) {
+                const float ku = to_f32(row[k_off + f]), kv = to_f32(row[k_off + i1]);
+                ks[a0] = (ku * cs - kv * sn) * k_scale;
+                ks[a1] = (kv * cs + ku * sn) * k_scale;
+            }
+        }
+        // what lies beyond the rotated coordinates passes as it is
+#pragma unroll 4
+        for (int idx = tid; idx < cn * (D - n_rot); idx += RT_THREADS) {
+            const int tt = idx / (D - n_rot), i = n_rot + idx % (D - n_rot);
+            const TA* row = proj + (size_t)(row0 + c0 + tt) * ld + (size_t)h * D;
+            if (!ZLM_CHK(row + q_off + i, sizeof(TA)) || !ZLM_CHK(row + k_off + i, sizeof(TA))) continue;
+            const int at = tt * DP + (i / DPT) * (DPT + 4) + i % DPT;
+            qs[at] = to_f32(row[q_off + i]);
+            if (MODE != 2) ks[at] = to_f32(row[k_off + i]) * k_scale;
         }
         if (MODE != 2)
+#pragma unroll 4
             for (int idx = tid; idx < cn * cols; idx += RT_THREADS) {
                 const int tt = idx / cols, cc = idx % cols, gc = blockIdx.x * cols + cc;
                 const TA* vp = proj + (size_t)(row0 + c0 + tt) * ld + v_off + (size_t)h * V + gc;
@@ -96,72 +140,125 @@ retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int
             }
         __syncthreads();
         for (int tt = 0; tt < cn; ++tt) {
-            float acc = 0.f;
-            const float* qr = qs + tt * D + part * DPT;
-            if (MODE == 2) {
-#pragma unroll
-                for (int j = 0; j < DPT; ++j)
-                    if (part * DPT + j < D) acc = fmaf(S[j], qr[j], acc);
-                acc *= dp;
-                dp *= d;
-            } else {
-                const float* kr = ks + tt * D + part * DPT;
-                const float v = vs[tt * cols + tid / ds];
-#pragma unroll
-                for (int j = 0; j < DPT; ++j)
-                    if (part * DPT + j < D) {
-                        S[j] = fmaf(d, S[j], kr[j] * v);
-                        acc = fmaf(S[j], qr[j], acc);
-                    }
+            float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            const float* qr = qs + tt * DP + part * (DPT + 4);
+            const float* kr = ks + tt * DP + part * (DPT + 4);
+            float2 v2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            if (MODE != 2) {
+                const float4 a = *(const float4*)(vs + tt * cols + grp * RT_CPT);
+                v2[0] = make_float2(a.x, a.y);
+                v2[1] = make_float2(a.z, a.w);
             }
-            for (int off = ds >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            float* op = o + (size_t)(row0 + c0 + tt) * H * V + (size_t)h * V + col;
-            if (part == 0 && live && ZLM_CHK(op, 4)) {
-                if (MODE == 2) *op += acc;
-                else *op = acc;
+            const float2 d2 = make_float2(d, d);
+            // (rows beyond D hold zeros in S and are staged as whatever the padding holds: they are passed over)
+#pragma unroll
+            for (int j = 0; j < DPT; j += 4) {
+                if (part * DPT + j >= D) break;
+                const float4 qa = *(const float4*)(qr + j);
+                const float q4[4] = {qa.x, qa.y, qa.z, qa.w};
+                float k4[4] = {0.f, 0.f, 0.f, 0.f};
+                if (MODE != 2) {
+                    const float4 ka = *(const float4*)(kr + j);
+                    k4[0] = ka.x; k4[1] = ka.y; k4[2] = ka.z; k4[3] = ka.w;
+                }
+                // S = d S + k v and o += S q, two columns an instruction (each element rounded as fmaf and a product
+                // would round it)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (part * DPT + j + e >= D) continue;
+                    const float2 kk = make_float2(k4[e], k4[e]), qq = make_float2(q4[e], q4[e]);
+#pragma unroll
+                    for (int c = 0; c < RT_CPT / 2; ++c) {
+                        if (MODE != 2) S[j + e][c] = __ffma2_rn(d2, S[j + e][c], __fmul2_rn(kk, v2[c]));
+                        acc2[c] = __ffma2_rn(S[j + e][c], qq, acc2[c]);
+                    }
+                }
+            }
+            float acc[RT_CPT] = {acc2[0].x, acc2[0].y, acc2[1].x, acc2[1].y};
+#pragma unroll
+            for (int c = 0; c < RT_CPT; ++c) {
+                if (MODE == 2) acc[c] *= dp;
+                for (int off = ds >> 1; off > 0; off >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], off);
+            }
+            if (MODE == 2) dp *= d;
+            float* op = o + (size_t)(row0 + c0 + tt) * H * V + (size_t)h * V + col0;
+            if (part == 0) {
+                if (v4 && ((size_t)H * V & 3) == 0 && ZLM_CHK(op, 16)) {
+                    float4 w = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                    if (MODE == 2) {
+                        const float4 old = *(const float4*)op;
+                        w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
+                    }
+                    *(float4*)op = w;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < RT_CPT; ++c)
+                        if (col0 + c < V && ZLM_CHK(op + c, 4)) op[c] = MODE == 2 ? op[c] + acc[c] : acc[c];
+                }
             }
         }
     }
-    if (MODE != 2 && live) {
+    if (MODE != 2) {
 #pragma unroll
         for (int j = 0; j < DPT; ++j) {
             const int i = part * DPT + j;
-            if (i < D && ZLM_CHK(sp + (size_t)i * V + col, 4)) sp[(size_t)i * V + col] = S[j];
+            if (i >= D) continue;
+            float* dst = sp + (size_t)i * V + col0;
+            if (v4 && ZLM_CHK(dst, 16)) {
+                *(float4*)dst = make_float4(S[j][0].x, S[j][0].y, S[j][1].x, S[j][1].y);
+            } else {
+                const float t[RT_CPT] = {S[j][0].x, S[j][0].y, S[j][1].x, S[j][1].y};
+#pragma unroll
+                for (int c = 0; c < RT_CPT; ++c)
+                    if (col0 + c < V && ZLM_CHK(dst + c, 4)) dst[c] = t[c];
+            }
         }
     }
 }
 
 // chains the pieces' states of one sequence: before[c] = S_(c-1), S_c = decay^len_c * S_(c-1) + part[c]; the last S
-// becomes the sequence's state.  grid (ceil(D*V / 256), H, R); the pieces of sequence r are seq_piece0[r] .. seq_piece0[r+1]-1
-// and `part_state` is overwritten in place by `before`.
+// becomes the sequence's state.  grid (ceil(D*V / 256), H, R); the pieces of sequence r are r * maxp .. and `part_state`
+// is overwritten in place by `before`.
 __global__ void __launch_bounds__(256)
 retention_chain_kernel(float* __restrict__ part_state, float* __restrict__ state, const float* __restrict__ decay,
-                       const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
-                       const int* __restrict__ seq_piece0, int piece, int H, int DV) {
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int maxp, int piece, int H,
+                       int DV) {
     pdl_launch_dependents();
     const int e = blockIdx.x * 256 + threadIdx.x, h = blockIdx.y, r = blockIdx.z;
     pdl_wait();
     if (e >= DV) return;
     const int n = cu_seqlens[r + 1] - cu_seqlens[r];
-    const int p0 = seq_piece0[r], np = seq_piece0[r + 1] - p0;
+    const int p0 = r * maxp, np = (n + piece - 1) / piece;
     float* sp = state + ((size_t)seq_slot[r] * H + h) * DV + e;
     if (!ZLM_CHK(sp, 4)) return;
     float S = *sp;
     const float d = decay[h];
-    for (int c = 0; c < np; ++c) {
-        float* pp = part_state + ((size_t)(p0 + c) * H + h) * DV + e;
-        if (!ZLM_CHK(pp, 4)) continue;
-        const int len = min(piece, n - c * piece);
-        const float a = *pp;
-        *pp = S;
-        S = fmaf(powf(d, (float)len), S, a);
+    const float dl = powf(d, (float)piece);            // every piece but the last is whole
+    for (int c0 = 0; c0 < np; c0 += 8) {
+        // eight pieces' states at a time: their loads do not wait for each other
+        float a[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float* pp = part_state + ((size_t)(p0 + c0 + u) * H + h) * DV + e;
+            a[u] = (c0 + u < np && ZLM_CHK(pp, 4)) ? *pp : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int c = c0 + u;
+            if (c >= np) break;
+            float* pp = part_state + ((size_t)(p0 + c) * H + h) * DV + e;
+            if (ZLM_CHK(pp, 4)) *pp = S;
+            const int len = min(piece, n - c * piece);
+            S = fmaf(len == piece ? dl : powf(d, (float)len), S, a[u]);
+        }
     }
     *sp = S;
 }
 
 static int retention_dpt(int D, int* ds) {
-    // rows of a column per thread: 32 where that leaves at most 8 threads a column, else more
-    int dpt = D <= 32 ? 32 : (D <= 256 ? 32 : 64);
+    // rows of the state a thread holds (times four columns, all in registers): 16 where 32 lanes of 16 hold a head's
+    // rows (about 110 registers a thread: four blocks an SM), else 32; heads of more than 1024 rows are refused
+    int dpt = D <= 512 ? 16 : 32;
     int n = (D + dpt - 1) / dpt, p = 1;
     while (p < n) p <<= 1;
     *ds = p;
@@ -171,8 +268,8 @@ static int retention_dpt(int D, int* ds) {
 template <typename TA, int MODE>
 static int launch_retention(dim3 grid, size_t smem, cudaStream_t st, int dpt, float* o, const void* proj, int ld, int q_off,
                             int k_off, int v_off, const float* inv_freq, int n_rot, const float* decay, float* state,
-                            const int* cu_seqlens, const int* seq_slot, const int* seq_start, const int* piece_seq,
-                            const int* piece_first, int piece, int H, int D, int V, int ds, float k_scale) {
+                            const int* cu_seqlens, const int* seq_slot, const int* seq_start, int maxp, int piece, int H, int D,
+                            int V, int ds, float k_scale, const float* table, int T, int chunk) {
 #define ZLM_RT_LAUNCH(DPT)                                                                                                \
     {                                                                                                                     \
         auto kern = retention_kernel<TA, DPT, MODE>;                                                                      \
@@ -186,10 +283,11 @@ static int launch_retention(dim3 grid, size_t smem, cudaStream_t st, int dpt, fl
             attr_set = true;                                                                                              \
         }                                                                                                                 \
         zlm_launch(kern, grid, dim3(RT_THREADS), smem, st, o, (const TA*)proj, ld, q_off, k_off, v_off, inv_freq, n_rot,   \
-                   decay, state, cu_seqlens, seq_slot, seq_start, piece_seq, piece_first, piece, H, D, V, ds, k_scale);    \
+                   decay, state, cu_seqlens, seq_slot, seq_start, maxp, piece, H, D, V, ds, k_scale,                      \
+                   table, T, chunk);                                                                                      \
     }
     if (dpt == 32) ZLM_RT_LAUNCH(32)
-    else ZLM_RT_LAUNCH(64)
+    else ZLM_RT_LAUNCH(16)
 #undef ZLM_RT_LAUNCH
     return ZLM_OK;
 }
@@ -201,63 +299,74 @@ static int retention_check(int H, int D, int V, int n_rot, int R) {
 }
 
 // o [T][H*V] fp32; proj [T][ld] with q at column q_off (H heads of D), k at k_off, v at v_off (H heads of V);
-// state [slots][H][D][V] fp32 (zero for a new sequence)
+// state [slots][H][D][V] fp32 (zero for a new sequence); table: the step's cosines and sines [2][n_rot/2][T] if they were
+// computed beforehand (else the kernel forms them from inv_freq)
 extern "C" int zlm_retention(float* o, const void* proj, int ld, int q_off, int k_off, int v_off, int dtype,
                              const float* inv_freq, int n_rot, const float* decay, float* state, const int* cu_seqlens,
                              const int* seq_slot, const int* seq_start, int R, int H, int D, int V, float k_scale,
-                             cudaStream_t st) {
+                             const float* table, int T, int max_new, cudaStream_t st) {
     if (R == 0) return ZLM_OK;
     int rc = retention_check(H, D, V, n_rot, R);
     if (rc) return rc;
     int ds;
     const int dpt = retention_dpt(D, &ds);
-    const int cols = RT_THREADS / ds;
-    const size_t smem = (size_t)RT_CHUNK * (2 * D + cols) * sizeof(float);
+    const int cols = RT_THREADS / ds * RT_CPT;
+    // tokens staged at a time: as many as fit in about 56 KB (four blocks an SM), at least 4
+    const size_t row_bytes = (size_t)(2 * ds * (dpt + 4) + cols) * sizeof(float);
+    int chunk = (int)((56 * 1024) / row_bytes);
+    chunk = chunk > RT_CHUNK ? RT_CHUNK : (chunk < 4 ? 4 : chunk);
+    if (max_new > 0 && chunk > max_new) chunk = max_new;          // (the longest sequence of the step: a decode step stages one token)
+    const size_t smem = (size_t)chunk * row_bytes;
     const dim3 grid((V + cols - 1) / cols, H, R);
     if (dtype == ZLM_DTYPE_F32)
         rc = launch_retention<float, 0>(grid, smem, st, dpt, o, proj, ld, q_off, k_off, v_off, inv_freq, n_rot, decay, state,
-                                        cu_seqlens, seq_slot, seq_start, nullptr, nullptr, 0, H, D, V, ds, k_scale);
+                                        cu_seqlens, seq_slot, seq_start, 0, 0, H, D, V, ds, k_scale, table, T, chunk);
     else if (dtype == ZLM_DTYPE_BF16)
         rc = launch_retention<__nv_bfloat16, 0>(grid, smem, st, dpt, o, proj, ld, q_off, k_off, v_off, inv_freq, n_rot, decay,
-                                                state, cu_seqlens, seq_slot, seq_start, nullptr, nullptr, 0, H, D, V, ds, k_scale);
+                                                state, cu_seqlens, seq_slot, seq_start, 0, 0, H, D, V, ds, k_scale, table, T, chunk);
     else
         ZLM_REQUIRE(false, "retention: unsupported dtype %d", dtype);
     if (rc) return rc;
     return zlm_check_launch("retention");
 }
 
-// The same for long prompts, in pieces of `piece` tokens that run side by side.  The host lists the pieces:
-// piece_seq / piece_first [pieces] (the sequence of a piece and its first token within the sequence's tokens of
-// this step), seq_piece0 [R + 1] (a sequence's first piece); part_state is scratch of pieces * H * D * V floats.
+// The same for long prompts, in pieces of `piece` tokens that run side by side: maxp pieces a sequence (those of the
+// step's longest one; a shorter sequence's last pieces are empty); part_state is scratch of R * maxp * H * D * V floats.
 extern "C" int zlm_retention_parts(float* o, const void* proj, int ld, int q_off, int k_off, int v_off, int dtype,
                                    const float* inv_freq, int n_rot, const float* decay, float* state,
-                                   const int* cu_seqlens, const int* seq_slot, const int* seq_start, int R,
-                                   const int* piece_seq, const int* piece_first, const int* seq_piece0, int pieces, int piece,
-                                   float* part_state, int H, int D, int V, float k_scale, cudaStream_t st) {
-    if (R == 0 || pieces == 0) return ZLM_OK;
+                                   const int* cu_seqlens, const int* seq_slot, const int* seq_start, int R, int maxp, int piece,
+                                   float* part_state, int H, int D, int V, float k_scale, const float* table, int T,
+                                   cudaStream_t st) {
+    if (R == 0 || maxp == 0) return ZLM_OK;
+    const long long pieces = (long long)R * maxp;
     int rc = retention_check(H, D, V, n_rot, R);
     if (rc) return rc;
-    ZLM_REQUIRE(piece > 0 && pieces <= 65535 && part_state, "retention: %d pieces of %d tokens", pieces, piece);
+    ZLM_REQUIRE(piece > 0 && pieces <= 65535 && part_state, "retention: %lld pieces of %d tokens", pieces, piece);
     int ds;
     const int dpt = retention_dpt(D, &ds);
-    const int cols = RT_THREADS / ds;
-    const size_t smem = (size_t)RT_CHUNK * (2 * D + cols) * sizeof(float);
-    const dim3 grid((V + cols - 1) / cols, H, pieces);
+    const int cols = RT_THREADS / ds * RT_CPT;
+    // tokens staged at a time: as many as fit in about 56 KB (four blocks an SM), at least 4
+    const size_t row_bytes = (size_t)(2 * ds * (dpt + 4) + cols) * sizeof(float);
+    int chunk = (int)((56 * 1024) / row_bytes);
+    chunk = chunk > RT_CHUNK ? RT_CHUNK : (chunk < 4 ? 4 : chunk);
+    if (chunk > piece) chunk = piece;
+    const size_t smem = (size_t)chunk * row_bytes;
+    const dim3 grid((V + cols - 1) / cols, H, (unsigned)pieces);
     for (int mode = 1; mode <= 2; ++mode) {
         if (dtype == ZLM_DTYPE_F32) {
             rc = mode == 1 ? launch_retention<float, 1>(grid, smem, st, dpt, o, proj, ld, q_off, k_off, v_off, inv_freq, n_rot, decay,
-                                                        part_state, cu_seqlens, seq_slot, seq_start, piece_seq, piece_first, piece,
-                                                        H, D, V, ds, k_scale)
+                                                        part_state, cu_seqlens, seq_slot, seq_start, maxp, piece,
+                                                        H, D, V, ds, k_scale, table, T, chunk)
                            : launch_retention<float, 2>(grid, smem, st, dpt, o, proj, ld, q_off, k_off, v_off, inv_freq, n_rot, decay,
-                                                        part_state, cu_seqlens, seq_slot, seq_start, piece_seq, piece_first, piece,
-                                                        H, D, V, ds, k_scale);
+                                                        part_state, cu_seqlens, seq_slot, seq_start, maxp, piece,
+                                                        H, D, V, ds, k_scale, table, T, chunk);
         } else if (dtype == ZLM_DTYPE_BF16) {
             rc = mode == 1 ? launch_retention<__nv_bfloat16, 1>(grid, smem, st, dpt, o, proj, ld, q_off, k_off, v_off, inv_freq,
                                                                 n_rot, decay, part_state, cu_seqlens, seq_slot, seq_start,
-                                                                piece_seq, piece_first, piece, H, D, V, ds, k_scale)
+                                                                maxp, piece, H, D, V, ds, k_scale, table, T, chunk)
                            : launch_retention<__nv_bfloat16, 2>(grid, smem, st, dpt, o, proj, ld, q_off, k_off, v_off, inv_freq,
                                                                 n_rot, decay, part_state, cu_seqlens, seq_slot, seq_start,
-                                                                piece_seq, piece_first, piece, H, D, V, ds, k_scale);
+                                                                maxp, piece, H, D, V, ds, k_scale, table, T, chunk);
         } else {
             ZLM_REQUIRE(false, "retention: unsupported dtype %d", dtype);
         }
@@ -266,7 +375,7 @@ extern "C" int zlm_retention_parts(float* o, const void* proj, int ld, int q_off
         if (rc) return rc;
         if (mode == 1) {
             zlm_launch(retention_chain_kernel, dim3((D * V + 255) / 256, H, R), dim3(256), 0, st, part_state, state, decay,
-                       cu_seqlens, seq_slot, seq_piece0, piece, H, D * V);
+                       cu_seqlens, seq_slot, maxp, piece, H, D * V);
             rc = zlm_check_launch("retention_chain");
             if (rc) return rc;
         }

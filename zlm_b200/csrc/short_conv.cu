@@ -19,7 +19,36 @@
 #define SC_MAX_TAPS 8
 #define SC_MAX_PER_LANE 16      // head sizes up to 512
 
-template <typename TA>
+// VEC consecutive elements as floats, and back (VEC 4: one 8- or 16-byte access; the caller has checked the alignment)
+template <typename TA, int VEC>
+__device__ __forceinline__ void load_vec(const TA* __restrict__ p, float* f) {
+    if (VEC == 1) {
+        f[0] = to_f32(p[0]);
+    } else if (sizeof(TA) == 2) {
+        const uint2 u = *(const uint2*)p;
+        f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+        f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+    } else {
+        const float4 v = *(const float4*)p;
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+}
+template <typename TA, int VEC>
+__device__ __forceinline__ void store_vec(TA* __restrict__ p, const float* f) {
+    if (VEC == 1) {
+        p[0] = from_f32<TA>(f[0]);
+    } else if (sizeof(TA) == 2) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+        uint2 u;
+        u.x = *(unsigned*)&a; u.y = *(unsigned*)&b;
+        *(uint2*)p = u;
+    } else {
+        *(float4*)p = make_float4(f[0], f[1], f[2], f[3]);
+    }
+}
+
+// a warp per head (q, k or v) of one token; a lane owns VEC neighbouring channels at a time
+template <typename TA, int VEC>
 __global__ void __launch_bounds__(SC_WARPS * 32)
 conv_norm_write_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __restrict__ proj, int proj_stride,
                        const TA* __restrict__ conv_w, const TA* __restrict__ state, const int* __restrict__ token_pos,
@@ -27,6 +56,7 @@ conv_norm_write_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __res
                        const int* __restrict__ seq_start, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ block_table, int table_stride, TA* __restrict__ pool, int nq, int nkv,
                        int dim, int vdim, int hdp, int taps, int norm, float eps) {
+    constexpr int ITER = SC_MAX_PER_LANE / VEC;
     pdl_trigger();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int unit = blockIdx.y * SC_WARPS + warp;
@@ -42,25 +72,28 @@ conv_norm_write_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __res
     const int width = kind == 2 ? vdim : dim;
     const int c0 = kind == 0 ? unit * dim : (kind == 1 ? nq * dim + (unit - nq) * dim : (nq + nkv) * dim + (unit - nq - nkv) * vdim);
 
-    float val[SC_MAX_PER_LANE];
+    float val[ITER][VEC];
     float ss = 0.f;
 #pragma unroll
-    for (int rr = 0; rr < SC_MAX_PER_LANE; ++rr) {
-        const int e = lane + 32 * rr;
-        val[rr] = 0.f;
+    for (int rr = 0; rr < ITER; ++rr) {
+        const int e = (lane + 32 * rr) * VEC;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) val[rr][v] = 0.f;
         if (e >= width) continue;
         const int c = c0 + e;
-        float y = 0.f;
         for (int j = 0; j < taps; ++j) {
             const int s = i - (taps - 1) + j;
             if (pos - (taps - 1) + j < 0) continue;                       // before the sequence's start
             const TA* up = s >= 0 ? proj + (size_t)(row0 + s) * proj_stride + c
                                   : state + ((size_t)slot * (taps - 1) + (taps - 1 + s)) * C + c;
-            if (!ZLM_CHK(up, sizeof(TA)) || !ZLM_CHK(conv_w + (size_t)c * taps + j, sizeof(TA))) continue;
-            y = fmaf(to_f32(conv_w[(size_t)c * taps + j]), to_f32(*up), y);
+            if (!ZLM_CHK(up, VEC * sizeof(TA)) || !ZLM_CHK(conv_w + (size_t)c * taps, (size_t)VEC * taps * sizeof(TA))) continue;
+            float u[VEC];
+            load_vec<TA, VEC>(up, u);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) val[rr][v] = fmaf(to_f32(conv_w[(size_t)(c + v) * taps + j]), u[v], val[rr][v]);
         }
-        val[rr] = y;
-        ss = fmaf(y, y, ss);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) ss = fmaf(val[rr][v], val[rr][v], ss);
     }
     float scale = 1.0f;
     if (norm && kind != 2) {
@@ -78,9 +111,13 @@ conv_norm_write_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __res
     }
     if (!ZLM_CHK(dst, (size_t)hdp * sizeof(TA))) return;
 #pragma unroll
-    for (int rr = 0; rr < SC_MAX_PER_LANE; ++rr) {
-        const int e = lane + 32 * rr;
-        if (e < hdp) dst[e] = from_f32<TA>(e < width ? val[rr] * scale : 0.f);
+    for (int rr = 0; rr < ITER; ++rr) {
+        const int e = (lane + 32 * rr) * VEC;
+        if (e >= hdp) continue;
+        float o[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) o[v] = e + v < width ? val[rr][v] * scale : 0.f;       // (width and hdp are multiples of VEC)
+        store_vec<TA, VEC>(dst + e, o);
     }
 }
 
@@ -114,10 +151,22 @@ static void launch_conv(void* q_out, int q_out_stride, const void* proj, int pro
                         int T, int R, int nq, int nkv, int dim, int vdim, int hdp, int taps, int norm, float eps,
                         cudaStream_t st) {
     const int units = nq + 2 * nkv;
-    zlm_launch(conv_norm_write_kernel<TA>, dim3(T, (units + SC_WARPS - 1) / SC_WARPS), dim3(SC_WARPS * 32), 0, st,
-               (TA*)q_out, q_out_stride, (const TA*)proj, proj_stride, (const TA*)conv_w, (const TA*)state, token_pos,
-               token_slot, token_seq, seq_start, cu_seqlens, block_table, table_stride, (TA*)pool, nq, nkv, dim, vdim, hdp,
-               taps, norm, eps);
+    const int C0 = (nq + nkv) * dim + nkv * vdim;
+    // four neighbouring channels a lane where every row and head starts at a multiple of four elements, 8 or 16 bytes
+    const size_t al = 4 * sizeof(TA);
+    const bool vec = dim % 4 == 0 && vdim % 4 == 0 && hdp % 4 == 0 && proj_stride % 4 == 0 && q_out_stride % 4 == 0 && C0 % 4 == 0 &&
+                     (uintptr_t)proj % al == 0 && (uintptr_t)q_out % al == 0 && (uintptr_t)pool % al == 0 &&
+                     (state == nullptr || (uintptr_t)state % al == 0);
+    if (vec)
+        zlm_launch(conv_norm_write_kernel<TA, 4>, dim3(T, (units + SC_WARPS - 1) / SC_WARPS), dim3(SC_WARPS * 32), 0, st,
+                   (TA*)q_out, q_out_stride, (const TA*)proj, proj_stride, (const TA*)conv_w, (const TA*)state, token_pos,
+                   token_slot, token_seq, seq_start, cu_seqlens, block_table, table_stride, (TA*)pool, nq, nkv, dim, vdim, hdp,
+                   taps, norm, eps);
+    else
+        zlm_launch(conv_norm_write_kernel<TA, 1>, dim3(T, (units + SC_WARPS - 1) / SC_WARPS), dim3(SC_WARPS * 32), 0, st,
+                   (TA*)q_out, q_out_stride, (const TA*)proj, proj_stride, (const TA*)conv_w, (const TA*)state, token_pos,
+                   token_slot, token_seq, seq_start, cu_seqlens, block_table, table_stride, (TA*)pool, nq, nkv, dim, vdim, hdp,
+                   taps, norm, eps);
     if (taps > 1) {
         const int C = (nq + nkv) * dim + nkv * vdim;
         zlm_launch(conv_state_update_kernel<TA>, dim3(R, (C + 255) / 256), dim3(256), 0, st, (TA*)state, (const TA*)proj,
@@ -158,10 +207,11 @@ extern "C" int zlm_conv_norm_write(void* q_out, int q_out_stride, const void* pr
 // out[t][h*V + e] = unit_norm?(o[t][h][:V])[e] * act(g[t][h*V + e]): the heads of a mixer's output, each optionally
 // divided by its root mean square (fp32), times sigmoid (act 0) or silu (act 1) of a gate projection, written
 // without the heads' padding.  o may be fp32 whatever the element type (a recurrence's output).
-template <typename TO, typename TA>
+template <typename TO, typename TA, int VEC>
 __global__ void __launch_bounds__(SC_WARPS * 32)
 head_gate_kernel(TA* __restrict__ out, int out_stride, const TO* __restrict__ o, int o_stride, int o_head_stride,
                  const TA* __restrict__ g, int g_stride, int H, int V, int norm, float eps, int act) {
+    constexpr int ITER = SC_MAX_PER_LANE / VEC;
     pdl_trigger();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y * SC_WARPS + warp;
@@ -172,23 +222,32 @@ head_gate_kernel(TA* __restrict__ out, int out_stride, const TO* __restrict__ o,
     TA* dst = out + (size_t)t * out_stride + (size_t)h * V;
     if (!ZLM_CHK(op, (size_t)V * sizeof(TO)) || !ZLM_CHK(gp, (size_t)V * sizeof(TA)) || !ZLM_CHK(dst, (size_t)V * sizeof(TA)))
         return;
-    float val[SC_MAX_PER_LANE];
+    float val[ITER][VEC];
     float ss = 0.f;
 #pragma unroll
-    for (int rr = 0; rr < SC_MAX_PER_LANE; ++rr) {
-        const int e = lane + 32 * rr;
-        val[rr] = e < V ? to_f32(op[e]) : 0.f;
-        ss = fmaf(val[rr], val[rr], ss);
+    for (int rr = 0; rr < ITER; ++rr) {
+        const int e = (lane + 32 * rr) * VEC;
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) val[rr][v] = 0.f;
+        if (e >= V) continue;
+        load_vec<TO, VEC>(op + e, val[rr]);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) ss = fmaf(val[rr][v], val[rr][v], ss);
     }
     float scale = 1.0f;
     if (norm) scale = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
 #pragma unroll
-    for (int rr = 0; rr < SC_MAX_PER_LANE; ++rr) {
-        const int e = lane + 32 * rr;
+    for (int rr = 0; rr < ITER; ++rr) {
+        const int e = (lane + 32 * rr) * VEC;
         if (e >= V) continue;
-        const float z = to_f32(gp[e]);
-        const float sg = 1.0f / (1.0f + expf(-z));
-        dst[e] = from_f32<TA>(val[rr] * scale * (act == 1 ? z * sg : sg));
+        float z[VEC], y[VEC];
+        load_vec<TA, VEC>(gp + e, z);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            const float sg = 1.0f / (1.0f + expf(-z[v]));
+            y[v] = val[rr][v] * scale * (act == 1 ? z[v] * sg : sg);
+        }
+        store_vec<TA, VEC>(dst + e, y);
     }
 }
 
@@ -200,17 +259,22 @@ extern "C" int zlm_head_gate(void* out, int out_stride, const void* o, int o_is_
                 "head_gate: %d heads of %d columns (at most %d)", H, V, 32 * SC_MAX_PER_LANE);
     ZLM_REQUIRE(act == 0 || act == 1, "head_gate: activation %d", act);
     const dim3 grid(T, (H + SC_WARPS - 1) / SC_WARPS), block(SC_WARPS * 32);
-    if (dtype == ZLM_DTYPE_F32)
-        zlm_launch(head_gate_kernel<float, float>, grid, block, 0, st, (float*)out, out_stride, (const float*)o, o_stride,
-                   o_head_stride, (const float*)g, g_stride, H, V, norm, eps, act);
-    else if (dtype == ZLM_DTYPE_BF16 && o_is_f32)
-        zlm_launch(head_gate_kernel<float, __nv_bfloat16>, grid, block, 0, st, (__nv_bfloat16*)out, out_stride,
-                   (const float*)o, o_stride, o_head_stride, (const __nv_bfloat16*)g, g_stride, H, V, norm, eps, act);
-    else if (dtype == ZLM_DTYPE_BF16)
-        zlm_launch(head_gate_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, st, (__nv_bfloat16*)out, out_stride,
-                   (const __nv_bfloat16*)o, o_stride, o_head_stride, (const __nv_bfloat16*)g, g_stride, H, V, norm, eps, act);
-    else
+    // four neighbouring columns a lane where every row and head starts at a multiple of 16 bytes
+    const bool vec = V % 4 == 0 && out_stride % 4 == 0 && o_stride % 4 == 0 && o_head_stride % 4 == 0 && g_stride % 4 == 0 &&
+                     (uintptr_t)out % 16 == 0 && (uintptr_t)o % 16 == 0 && (uintptr_t)g % 16 == 0;
+#define ZLM_HG(TO, TA, VEC)                                                                                              \
+    zlm_launch(head_gate_kernel<TO, TA, VEC>, grid, block, 0, st, (TA*)out, out_stride, (const TO*)o, o_stride, o_head_stride, \
+               (const TA*)g, g_stride, H, V, norm, eps, act)
+    if (dtype == ZLM_DTYPE_F32) {
+        if (vec) ZLM_HG(float, float, 4); else ZLM_HG(float, float, 1);
+    } else if (dtype == ZLM_DTYPE_BF16 && o_is_f32) {
+        if (vec) ZLM_HG(float, __nv_bfloat16, 4); else ZLM_HG(float, __nv_bfloat16, 1);
+    } else if (dtype == ZLM_DTYPE_BF16) {
+        if (vec) ZLM_HG(__nv_bfloat16, __nv_bfloat16, 4); else ZLM_HG(__nv_bfloat16, __nv_bfloat16, 1);
+    } else {
         ZLM_REQUIRE(false, "head_gate: unsupported dtype %d", dtype);
+    }
+#undef ZLM_HG
     return zlm_check_launch("head_gate");
 }
 

@@ -726,11 +726,14 @@ class CudaKernels:
 
     def retention(self, o: torch.Tensor, proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
                   inv_freq: Optional[torch.Tensor], n_rot: int, decay: torch.Tensor, state: torch.Tensor, plan,
-                  heads: int, dim: int, v_dim: int, k_scale: float, pieces: Optional[bool] = None) -> None:
+                  heads: int, dim: int, v_dim: int, k_scale: float, pieces: Optional[bool] = None,
+                  cos_sin: Optional[torch.Tensor] = None) -> None:
         """o [T, heads*v_dim] fp32 = S_t^T q_t with S_t = decay_h S_(t-1) + k_t v_t^T per head, q and k rotated (first
         ``n_rot`` coordinates of a head, halves against each other, by pos * inv_freq) and k scaled by ``k_scale``; q, k,
         v are columns of ``proj`` from q_off, k_off, v_off on; ``state`` [slots, heads, dim, v_dim] fp32 holds S between
-        steps.  Long prompts run in pieces side by side (``pieces`` forces or forbids that)."""
+        steps.  Long prompts run in pieces side by side (``pieces`` forces or forbids that).  ``cos_sin``: the step's
+        rotation table [2, n_rot/2, T] (``rope_table``) where a step computes it once for all layers; without it the
+        kernel forms cosines and sines itself."""
         T = proj.shape[0]
         assert o.shape == (T, heads * v_dim) and o.dtype == torch.float32 and o.is_contiguous() and proj.stride(1) == 1
         assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dim, v_dim) and state.is_contiguous()
@@ -739,29 +742,23 @@ class CudaKernels:
             assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot
         else:
             n_rot = 0
+        if cos_sin is not None:
+            assert n_rot and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.numel() == T * n_rot
+        tail = (c_int(heads), c_int(dim), c_int(v_dim), c_float(k_scale), self._p(cos_sin), c_int(T), self._stream())
         head = (self._p(o), self._p(proj), c_int(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), c_int(_dt(proj)),
                 self._p(inv_freq if n_rot else None), c_int(n_rot), self._p(decay), self._p(state), self._p(plan.cu_seqlens),
                 self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R))
         if pieces is None:
             pieces = plan.max_new >= self.RETENTION_PIECES_FROM
         if pieces:
-            # the pieces of every sequence, listed on the host (a step's sequences and their lengths are known there)
+            # as many pieces a sequence as the longest one has (a shorter sequence's last pieces are empty): nothing
+            # about the step's sequences has to be carried to the device beyond what the step has there already
             L = self.RETENTION_PIECE
-            p_seq, p_first, s_p0 = [], [], [0]
-            for r, n in enumerate(plan.h_seq_new):
-                for f in range(0, n, L):
-                    p_seq.append(r)
-                    p_first.append(f)
-                s_p0.append(len(p_seq))
-            P = len(p_seq)
-            ints = plan.scratch("retention.pieces", (2 * P + len(s_p0),), torch.int32)
-            ints.copy_(torch.tensor(p_seq + p_first + s_p0, dtype=torch.int32), non_blocking=False)
-            part = plan.scratch("retention.part_state", (P * heads * dim * v_dim,), torch.float32)
-            self._call("zlm_retention_parts", *head, self._p(ints[:P]), self._p(ints[P:2 * P]), self._p(ints[2 * P:]),
-                       c_int(P), c_int(L), self._p(part), c_int(heads), c_int(dim), c_int(v_dim), c_float(k_scale),
-                       self._stream())
+            maxp = (int(plan.max_new) + L - 1) // L
+            part = plan.scratch("retention.part_state", (plan.R * maxp * heads * dim * v_dim,), torch.float32)
+            self._call("zlm_retention_parts", *head, c_int(maxp), c_int(L), self._p(part), *tail)
             return
-        self._call("zlm_retention", *head, c_int(heads), c_int(dim), c_int(v_dim), c_float(k_scale), self._stream())
+        self._call("zlm_retention", *head, *tail[:-1], c_int(int(getattr(plan, "max_new", 0) or 0)), tail[-1])
 
     # -- latent attention (see csrc/latent_attention.cu) --------------------
     def latent_prep(self, q: torch.Tensor, q_rot: torch.Tensor, dkv: Optional[torch.Tensor],

@@ -72,8 +72,11 @@ class Retention(Mixer):
         proj = rt.ws.get("retention.proj", (T, 2 * self.QK + 2 * self.VV), rt.dtype)
         k.linear(proj, x, self.w_in)
         o = rt.ws.get("retention.o", (T, self.VV), torch.float32)
+        # many tokens: the step's cosines and sines come from the table that the position encoding computes once a
+        # step for all layers with its frequencies; few tokens: the kernel forms its own
+        table = self.position.table(ctx) if (T > 16 and self.position.n_rot and hasattr(self.position, "table")) else None
         k.retention(o, proj, 0, self.QK, 2 * self.QK, self.position.inv_freq, self.position.n_rot, self.decay, io.state,
-                    ctx, self.H, self.D, self.V, self.k_scale)
+                    ctx, self.H, self.D, self.V, self.k_scale, cos_sin=table)
         y = rt.ws.get("retention.gated", (T, self.VV), rt.dtype)
         k.head_gate(y, o.view(T, self.H, self.V), proj[:, 2 * self.QK + self.VV:], self.H, self.V, True, self.eps, self.gate)
         k.linear(residual, y, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next

@@ -211,13 +211,13 @@ class ProfilingKernels:
                            norm, eps, act)
 
     def retention(self, o, proj, q_off, k_off, v_off, inv_freq, n_rot, decay, state, plan, heads, dim, v_dim, k_scale,
-                  pieces=None):
+                  pieces=None, cos_sin=None):
         T, el = proj.shape[0], proj.element_size()
         n = T * heads * (2 * dim + v_dim) * el + _nbytes(o) + 2 * plan.R * heads * dim * v_dim * 4
         kind = "retention decode" if plan.is_decode else "retention prefill"
         # (fp32 multiply-adds on the ordinary cores, not the tensor cores: state update and read-out)
         return self._timed(kind, n, 4.0 * T * heads * dim * v_dim, self.k.retention, o, proj, q_off, k_off, v_off, inv_freq,
-                           n_rot, decay, state, plan, heads, dim, v_dim, k_scale, pieces)
+                           n_rot, decay, state, plan, heads, dim, v_dim, k_scale, pieces, cos_sin)
 
     # latent attention and routed experts
     def latent_prep(self, q, q_rot, dkv, *args, **kw):
