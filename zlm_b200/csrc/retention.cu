@@ -66,29 +66,34 @@ retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int
     }
     const int row0 = cu_seqlens[r] + first, pos0 = seq_start[r] + first;
     const float d = decay[h];
-    float2 S[DPT][RT_CPT / 2];                // the tile, two neighbouring columns a register pair (packed fp32 arithmetic)
+    // the tile, two neighbouring rows a register pair (packed fp32 arithmetic: the pairs of q and k come straight
+    // from their 16-byte reads)
+    float2 S[DPT / 2][RT_CPT];
     float* sp = nullptr;
     if (MODE == 0) sp = state + ((size_t)seq_slot[r] * H + h) * D * V;
     else sp = state + ((size_t)blockIdx.z * H + h) * D * V;       // MODE 1: part_state (written); MODE 2: chain (read)
     const bool v4 = (V & 3) == 0 && col0 + RT_CPT <= V;             // the tile's columns as one 16-byte access
 #pragma unroll
-    for (int j = 0; j < DPT; ++j) {
-        const int i = part * DPT + j;
-        S[j][0] = S[j][1] = make_float2(0.f, 0.f);
-        if (MODE == 1 || i >= D) continue;
-        const float* src = sp + (size_t)i * V + col0;
-        if (v4 && ZLM_CHK(src, 16)) {
-            const float4 a = *(const float4*)src;
-            S[j][0] = make_float2(a.x, a.y);
-            S[j][1] = make_float2(a.z, a.w);
-        } else {
-            float t[RT_CPT] = {0.f, 0.f, 0.f, 0.f};
+    for (int jj = 0; jj < DPT / 2; ++jj) {
+        float t[2][RT_CPT];
 #pragma unroll
-            for (int c = 0; c < RT_CPT; ++c)
-                if (col0 + c < V && ZLM_CHK(src + c, 4)) t[c] = src[c];
-            S[j][0] = make_float2(t[0], t[1]);
-            S[j][1] = make_float2(t[2], t[3]);
+        for (int e = 0; e < 2; ++e) {
+            const int i = part * DPT + 2 * jj + e;
+#pragma unroll
+            for (int c = 0; c < RT_CPT; ++c) t[e][c] = 0.f;
+            if (MODE == 1 || i >= D) continue;
+            const float* src = sp + (size_t)i * V + col0;
+            if (v4 && ZLM_CHK(src, 16)) {
+                const float4 a = *(const float4*)src;
+                t[e][0] = a.x; t[e][1] = a.y; t[e][2] = a.z; t[e][3] = a.w;
+            } else {
+#pragma unroll
+                for (int c = 0; c < RT_CPT; ++c)
+                    if (col0 + c < V && ZLM_CHK(src + c, 4)) t[e][c] = src[c];
+            }
         }
+#pragma unroll
+        for (int c = 0; c < RT_CPT; ++c) S[jj][c] = make_float2(t[0][c], t[1][c]);
     }
     float dp = d;                              // MODE 2: decay^(j+1)
     const int half = n_rot >> 1;
@@ -131,6 +136,13 @@ retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int
             qs[at] = to_f32(row[q_off + i]);
             if (MODE != 2) ks[at] = to_f32(row[k_off + i]) * k_scale;
         }
+        // rows of the tiles beyond the head's own stay zero: the walk below asks no row whether it exists
+        for (int idx = tid; idx < cn * (ds * DPT - D); idx += RT_THREADS) {
+            const int tt = idx / (ds * DPT - D), i = D + idx % (ds * DPT - D);
+            const int at = tt * DP + (i / DPT) * (DPT + 4) + i % DPT;
+            qs[at] = 0.f;
+            ks[at] = 0.f;
+        }
         if (MODE != 2)
 #pragma unroll 4
             for (int idx = tid; idx < cn * cols; idx += RT_THREADS) {
@@ -140,79 +152,93 @@ retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int
             }
         __syncthreads();
         for (int tt = 0; tt < cn; ++tt) {
-            float2 acc2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            float2 acc2[RT_CPT];
+            float2 vv[RT_CPT];
+#pragma unroll
+            for (int c = 0; c < RT_CPT; ++c) acc2[c] = vv[c] = make_float2(0.f, 0.f);
             const float* qr = qs + tt * DP + part * (DPT + 4);
             const float* kr = ks + tt * DP + part * (DPT + 4);
-            float2 v2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
             if (MODE != 2) {
                 const float4 a = *(const float4*)(vs + tt * cols + grp * RT_CPT);
-                v2[0] = make_float2(a.x, a.y);
-                v2[1] = make_float2(a.z, a.w);
+                vv[0] = make_float2(a.x, a.x); vv[1] = make_float2(a.y, a.y);
+                vv[2] = make_float2(a.z, a.z); vv[3] = make_float2(a.w, a.w);
             }
             const float2 d2 = make_float2(d, d);
-            // (rows beyond D hold zeros in S and are staged as whatever the padding holds: they are passed over)
+            // S = d S + k v and o += S q, two rows an instruction (each element rounded as fmaf and a product would
+            // round it); acc2 holds the sums over a thread's even and odd rows
 #pragma unroll
             for (int j = 0; j < DPT; j += 4) {
-                if (part * DPT + j >= D) break;
                 const float4 qa = *(const float4*)(qr + j);
-                const float q4[4] = {qa.x, qa.y, qa.z, qa.w};
-                float k4[4] = {0.f, 0.f, 0.f, 0.f};
+                const float2 q2[2] = {make_float2(qa.x, qa.y), make_float2(qa.z, qa.w)};
+                float2 k2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
                 if (MODE != 2) {
                     const float4 ka = *(const float4*)(kr + j);
-                    k4[0] = ka.x; k4[1] = ka.y; k4[2] = ka.z; k4[3] = ka.w;
+                    k2[0] = make_float2(ka.x, ka.y);
+                    k2[1] = make_float2(ka.z, ka.w);
                 }
-                // S = d S + k v and o += S q, two columns an instruction (each element rounded as fmaf and a product
-                // would round it)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    if (part * DPT + j + e >= D) continue;
-                    const float2 kk = make_float2(k4[e], k4[e]), qq = make_float2(q4[e], q4[e]);
+                for (int e = 0; e < 2; ++e)
 #pragma unroll
-                    for (int c = 0; c < RT_CPT / 2; ++c) {
-                        if (MODE != 2) S[j + e][c] = __ffma2_rn(d2, S[j + e][c], __fmul2_rn(kk, v2[c]));
-                        acc2[c] = __ffma2_rn(S[j + e][c], qq, acc2[c]);
+                    for (int c = 0; c < RT_CPT; ++c) {
+                        if (MODE != 2) S[j / 2 + e][c] = __ffma2_rn(d2, S[j / 2 + e][c], __fmul2_rn(k2[e], vv[c]));
+                        acc2[c] = __ffma2_rn(S[j / 2 + e][c], q2[e], acc2[c]);
                     }
-                }
             }
-            float acc[RT_CPT] = {acc2[0].x, acc2[0].y, acc2[1].x, acc2[1].y};
+            float acc[RT_CPT];
 #pragma unroll
-            for (int c = 0; c < RT_CPT; ++c) {
-                if (MODE == 2) acc[c] *= dp;
-                for (int off = ds >> 1; off > 0; off >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], off);
-            }
+            for (int c = 0; c < RT_CPT; ++c) acc[c] = (acc2[c].x + acc2[c].y) * (MODE == 2 ? dp : 1.0f);
             if (MODE == 2) dp *= d;
-            float* op = o + (size_t)(row0 + c0 + tt) * H * V + (size_t)h * V + col0;
-            if (part == 0) {
-                if (v4 && ((size_t)H * V & 3) == 0 && ZLM_CHK(op, 16)) {
-                    float4 w = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                    if (MODE == 2) {
-                        const float4 old = *(const float4*)op;
-                        w.x += old.x; w.y += old.y; w.z += old.z; w.w += old.w;
-                    }
-                    *(float4*)op = w;
-                } else {
+            // the ds lanes of a tile add up their parts; while they do, the columns are dealt out among them (half of
+            // the lanes go on with columns 0-1, half with 2-3, then one column each), so that the sums cost 4 shuffles
+            // where 4 x log2(ds) would be the plain way.  `mine` is the first column a lane ends up with, `have` how many.
+            int mine = 0, have = RT_CPT;
+            if (ds >= 2) {
+                const int off = ds >> 1;
+                const bool up = (part & off) != 0;
+                const float s0 = up ? acc[0] : acc[2], s1 = up ? acc[1] : acc[3];
+                const float r0 = __shfl_xor_sync(0xffffffffu, s0, off), r1 = __shfl_xor_sync(0xffffffffu, s1, off);
+                acc[0] = (up ? acc[2] : acc[0]) + r0;
+                acc[1] = (up ? acc[3] : acc[1]) + r1;
+                mine = up ? 2 : 0;
+                have = 2;
+            }
+            if (ds >= 4) {
+                const int off = ds >> 2;
+                const bool up = (part & off) != 0;
+                const float r0 = __shfl_xor_sync(0xffffffffu, up ? acc[0] : acc[1], off);
+                acc[0] = (up ? acc[1] : acc[0]) + r0;
+                mine += up ? 1 : 0;
+                have = 1;
+                for (int o2 = ds >> 3; o2 > 0; o2 >>= 1) acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], o2);
+            }
+            // the lanes whose lower bits are zero write
+            const bool writer = ds < 8 || (part & ((ds >> 2) - 1)) == 0;
+            float* op = o + (size_t)(row0 + c0 + tt) * H * V + (size_t)h * V + col0 + mine;
+            if (writer) {
 #pragma unroll
-                    for (int c = 0; c < RT_CPT; ++c)
-                        if (col0 + c < V && ZLM_CHK(op + c, 4)) op[c] = MODE == 2 ? op[c] + acc[c] : acc[c];
-                }
+                for (int c = 0; c < RT_CPT; ++c)
+                    if (c < have && col0 + mine + c < V && ZLM_CHK(op + c, 4)) op[c] = MODE == 2 ? op[c] + acc[c] : acc[c];
             }
         }
     }
     if (MODE != 2) {
 #pragma unroll
-        for (int j = 0; j < DPT; ++j) {
-            const int i = part * DPT + j;
-            if (i >= D) continue;
-            float* dst = sp + (size_t)i * V + col0;
-            if (v4 && ZLM_CHK(dst, 16)) {
-                *(float4*)dst = make_float4(S[j][0].x, S[j][0].y, S[j][1].x, S[j][1].y);
-            } else {
-                const float t[RT_CPT] = {S[j][0].x, S[j][0].y, S[j][1].x, S[j][1].y};
+        for (int jj = 0; jj < DPT / 2; ++jj)
 #pragma unroll
-                for (int c = 0; c < RT_CPT; ++c)
-                    if (col0 + c < V && ZLM_CHK(dst + c, 4)) dst[c] = t[c];
+            for (int e = 0; e < 2; ++e) {
+                const int i = part * DPT + 2 * jj + e;
+                if (i >= D) continue;
+                float* dst = sp + (size_t)i * V + col0;
+                const float t[RT_CPT] = {e ? S[jj][0].y : S[jj][0].x, e ? S[jj][1].y : S[jj][1].x, e ? S[jj][2].y : S[jj][2].x,
+                                         e ? S[jj][3].y : S[jj][3].x};
+                if (v4 && ZLM_CHK(dst, 16)) {
+                    *(float4*)dst = make_float4(t[0], t[1], t[2], t[3]);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < RT_CPT; ++c)
+                        if (col0 + c < V && ZLM_CHK(dst + c, 4)) dst[c] = t[c];
+                }
             }
-        }
     }
 }
 
