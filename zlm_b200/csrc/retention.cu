@@ -102,7 +102,7 @@ retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int
         __syncthreads();
         // the chunk's q and k, rotated: a thread turns a pair (f, f + half) of a token at a time, so that the pair and
         // its cosine and sine are read once; the loads of several pairs are in flight together
-#pragma unroll 4
+#pragma unroll 8
         for (int idx = tid; idx < cn * half; idx += RT_THREADS) {
             const int tt = idx / half, f = idx % half;
             const int rowi = row0 + c0 + tt;
@@ -143,13 +143,23 @@ retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int
             qs[at] = 0.f;
             ks[at] = 0.f;
         }
-        if (MODE != 2)
-#pragma unroll 4
+        if (MODE != 2) {
+#pragma unroll 8
             for (int idx = tid; idx < cn * cols; idx += RT_THREADS) {
                 const int tt = idx / cols, cc = idx % cols, gc = blockIdx.x * cols + cc;
                 const TA* vp = proj + (size_t)(row0 + c0 + tt) * ld + v_off + (size_t)h * V + gc;
                 vs[tt * cols + cc] = (gc < V && ZLM_CHK(vp, sizeof(TA))) ? to_f32(*vp) : 0.f;
             }
+        } else {
+            // the outputs that the pieces' own walks left, to which this pass adds: staged like the values, so that the
+            // walk below does not wait for global memory at every token
+#pragma unroll 8
+            for (int idx = tid; idx < cn * cols; idx += RT_THREADS) {
+                const int tt = idx / cols, cc = idx % cols, gc = blockIdx.x * cols + cc;
+                const float* op = o + (size_t)(row0 + c0 + tt) * H * V + (size_t)h * V + gc;
+                vs[tt * cols + cc] = (gc < V && ZLM_CHK(op, 4)) ? *op : 0.f;
+            }
+        }
         __syncthreads();
         for (int tt = 0; tt < cn; ++tt) {
             float2 acc2[RT_CPT];
@@ -217,7 +227,8 @@ retention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int ld, int
             if (writer) {
 #pragma unroll
                 for (int c = 0; c < RT_CPT; ++c)
-                    if (c < have && col0 + mine + c < V && ZLM_CHK(op + c, 4)) op[c] = MODE == 2 ? op[c] + acc[c] : acc[c];
+                    if (c < have && col0 + mine + c < V && ZLM_CHK(op + c, 4))
+                        op[c] = MODE == 2 ? vs[tt * cols + grp * RT_CPT + mine + c] + acc[c] : acc[c];
             }
         }
     }
