@@ -51,7 +51,7 @@ def peaked_attention(window, conv=1, heads=2, kv_heads=2, dim=16, vdim=24, scale
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window", [0, 9, 64, 70, 136])
+@pytest.mark.parametrize("window", [0, 9, 64, 70, 150])
 def test_a_key_that_holds_the_weight_at_every_distance(tmp_path, dtype, window):
     """The key sits 1, 63, 64, 65 and several hundred tokens back, and just inside and just outside the window;
     the query is asked for inside a prompt, at the start of a portion, and decoded alone."""
