@@ -77,8 +77,11 @@ __device__ __forceinline__ void route_choose(float* sc, float* cs, float* gm, in
         float mx = -INFINITY;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
         mx = warp_max(mx);
-        float sum = 0.f;
-        for (int e = 0; e < E; ++e) sum += expf(sc[e] - mx);      // one order for all lanes
+        // every lane adds its share, then the lanes' sums meet in a butterfly: the same bits in every lane, in an
+        // order that depends on E alone
+        float part = 0.f;
+        for (int e = lane; e < E; e += 32) part += expf(sc[e] - mx);
+        const float sum = warp_sum(part);
         __syncwarp();
         for (int e = lane; e < E; e += 32) sc[e] = expf(sc[e] - mx) / sum;
         __syncwarp();
